@@ -1,0 +1,1114 @@
+// Sparse MoE decode reader for B200 (sm_100a): kernels and C ABI.
+//
+// One call processes T decode tokens of one MoE layer:
+//   prepare  rotate the input (block Hadamard), keep the KEEP largest rotated
+//            coordinates per 128-block, make a fixed-point copy of them
+//   route    sort each token's K experts ascending, map to local ids
+//   screen   exact integer dot products of the 2-bit ternary sketch with the
+//            fixed-point rotated input -> projections -> selection scores
+//   select   per token the F best scores (radix select), ties to the lower
+//            candidate index; read-cost counters
+//   exact    gathered BF16 gate/up rows of the kept channels, phi(g) * u
+//   down     gathered channel-major down rows of the kept channels
+//   encode   low-rank recovery encoder over the skipped channels
+//   output   router-weighted mix + decoder term, BF16 store
+//
+// Selection depends only on integer dot products and pinned FP32 operations
+// (see cfm_device.cuh), so it does not change with batch size, split count or
+// launch shape.  No kernel waits on another: cross-CTA reductions use the
+// "last CTA to arrive finishes" pattern with an atomic counter and no spin.
+#include "cfm_device.cuh"
+
+#include "cfm_b200.h"
+
+namespace cfm {
+
+// ---------------------------------------------------------------------------
+// Workspace binding
+// ---------------------------------------------------------------------------
+struct Workspace {
+  int32_t* ids;
+  float* weights;
+  float* norms;
+  float* planes;
+  int32_t* coordinates;
+  int32_t* quantized;
+  int32_t* exponents;
+  float* parts;
+  uint32_t* counters;
+  float* partial;
+  float* scores;
+  uint8_t* selected;
+  uint8_t* completed;
+  int32_t* candidate_ids;
+  int32_t* counts;
+  int32_t* starts;
+  int32_t* tile_starts;
+  __nv_bfloat16* activations;
+  float* exact;
+  float* down_parts;
+  float* encoder_parts;
+  float* latent;
+  int32_t* status;
+  int32_t parts_tokens;
+  int32_t down_tiles;
+  int32_t encoder_tiles;
+  int32_t capacity;
+};
+
+struct Layer {  // device-visible copy of cfm_layer with typed pointers
+  int H, I, E, K, F, KEEP, R, activation, score, global_experts, owner;
+  int B, N, W;  // blocks, candidates, sketch words per coordinate
+  const __nv_bfloat16* gate_up;
+  const __nv_bfloat16* down;
+  const uint32_t* sketch;
+  const __half* statistics;
+  const float* norms;
+  const float* geometry;
+  const __nv_bfloat16* encoder;
+  const __nv_bfloat16* decoder;
+  const int8_t* signs;
+  const int32_t* expert_map;
+  double* read_work;
+};
+
+static int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
+
+static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layout* o) {
+  if (!l || !o) return CFM_E_NULL;
+  const int64_t H = l->hidden, I = l->width, K = l->top_k, F = l->final_count;
+  const int64_t KEEP = l->keep, R = l->rank, C = capacity;
+  if (H <= 0 || H % kBlock || I <= 0 || I % 16 || K <= 0 || K > 32 || KEEP < 1 ||
+      KEEP > kBlock || R < 0 || R > 256 || (R % 8) || (R && (256 % R)) || F < 1 ||
+      F > K * I || K * I > 65535 * 16)
+    return CFM_E_SHAPE;
+  if (C < 1) return CFM_E_CAPACITY;
+  const int64_t B = H / kBlock, N = K * I;
+  int64_t at = 0;
+  auto take = [&](int64_t bytes) {
+    const int64_t here = at;
+    at = align256(at + bytes);
+    return here;
+  };
+  o->parts_tokens = static_cast<int32_t>(C < 16 ? C : 16);
+  o->down_tiles = static_cast<int32_t>((F + kDownTileRows - 1) / kDownTileRows + K - 1);
+  o->encoder_tiles = static_cast<int32_t>((I + kEncodeTileRows - 1) / kEncodeTileRows);
+  o->reserved = 0;
+  o->ids = take(4 * C * K);
+  o->weights = take(4 * C * K);
+  o->norms = take(4 * C * B);
+  o->planes = take(4 * C * B * KEEP);
+  o->coordinates = take(4 * C * B * KEEP);
+  o->quantized = take(4 * C * B * KEEP);
+  o->exponents = take(4 * C * B * 2);
+  o->parts = take(4 * o->parts_tokens * K * B * 2 * I);
+  o->counters = take(4 * (2 * C * K + 2 * C));
+  o->partial = take(4 * C * 2 * N);
+  o->scores = take(4 * C * N);
+  o->selected = take(C * N);
+  o->completed = take(C * N);
+  o->candidate_ids = take(4 * C * F);
+  o->counts = take(4 * C * K);
+  o->starts = take(4 * C * K);
+  o->tile_starts = take(4 * C * K);
+  o->activations = take(2 * C * N);
+  o->exact = take(4 * C * 2 * F);
+  o->down_parts = take(4 * C * o->down_tiles * H);
+  o->encoder_parts = take(4 * C * K * o->encoder_tiles * (R ? R : 1));
+  o->latent = take(4 * C * (R ? R : 1));
+  o->status = take(16);
+  o->bytes = at;
+  return 0;
+}
+
+static Workspace bind(const cfm_workspace_layout& o, void* base, int32_t capacity) {
+  char* p = static_cast<char*>(base);
+  Workspace w;
+  w.ids = reinterpret_cast<int32_t*>(p + o.ids);
+  w.weights = reinterpret_cast<float*>(p + o.weights);
+  w.norms = reinterpret_cast<float*>(p + o.norms);
+  w.planes = reinterpret_cast<float*>(p + o.planes);
+  w.coordinates = reinterpret_cast<int32_t*>(p + o.coordinates);
+  w.quantized = reinterpret_cast<int32_t*>(p + o.quantized);
+  w.exponents = reinterpret_cast<int32_t*>(p + o.exponents);
+  w.parts = reinterpret_cast<float*>(p + o.parts);
+  w.counters = reinterpret_cast<uint32_t*>(p + o.counters);
+  w.partial = reinterpret_cast<float*>(p + o.partial);
+  w.scores = reinterpret_cast<float*>(p + o.scores);
+  w.selected = reinterpret_cast<uint8_t*>(p + o.selected);
+  w.completed = reinterpret_cast<uint8_t*>(p + o.completed);
+  w.candidate_ids = reinterpret_cast<int32_t*>(p + o.candidate_ids);
+  w.counts = reinterpret_cast<int32_t*>(p + o.counts);
+  w.starts = reinterpret_cast<int32_t*>(p + o.starts);
+  w.tile_starts = reinterpret_cast<int32_t*>(p + o.tile_starts);
+  w.activations = reinterpret_cast<__nv_bfloat16*>(p + o.activations);
+  w.exact = reinterpret_cast<float*>(p + o.exact);
+  w.down_parts = reinterpret_cast<float*>(p + o.down_parts);
+  w.encoder_parts = reinterpret_cast<float*>(p + o.encoder_parts);
+  w.latent = reinterpret_cast<float*>(p + o.latent);
+  w.status = reinterpret_cast<int32_t*>(p + o.status);
+  w.parts_tokens = o.parts_tokens;
+  w.down_tiles = o.down_tiles;
+  w.encoder_tiles = o.encoder_tiles;
+  w.capacity = capacity;
+  return w;
+}
+
+static Layer device_layer(const cfm_layer* l) {
+  Layer d;
+  d.H = l->hidden;
+  d.I = l->width;
+  d.E = l->experts;
+  d.K = l->top_k;
+  d.F = l->final_count;
+  d.KEEP = l->keep;
+  d.R = l->rank;
+  d.activation = l->activation;
+  d.score = l->score;
+  d.global_experts = l->global_experts;
+  d.owner = l->recovery_owner;
+  d.B = d.H / kBlock;
+  d.N = d.K * d.I;
+  d.W = 2 * d.I / kWordRows;
+  d.gate_up = static_cast<const __nv_bfloat16*>(l->gate_up);
+  d.down = static_cast<const __nv_bfloat16*>(l->down);
+  d.sketch = l->sketch;
+  d.statistics = static_cast<const __half*>(l->statistics);
+  d.norms = l->norms;
+  d.geometry = l->geometry;
+  d.encoder = static_cast<const __nv_bfloat16*>(l->encoder);
+  d.decoder = static_cast<const __nv_bfloat16*>(l->decoder);
+  d.signs = l->signs;
+  d.expert_map = l->expert_map;
+  d.read_work = l->read_work;
+  return d;
+}
+
+// ---------------------------------------------------------------------------
+// prepare: rotation, partial-screen mask, fixed-point copy
+// ---------------------------------------------------------------------------
+// grid (T, B), 128 threads: one thread per coordinate of one rotation block.
+__global__ void __launch_bounds__(kBlock) k_prepare(Layer L, Workspace ws,
+                                                    const __nv_bfloat16* hidden,
+                                                    const uint8_t* padding) {
+  const int t = blockIdx.x, b = blockIdx.y, c = threadIdx.x;
+  if (padding && padding[t]) return;
+  __shared__ float sm[kBlock];
+  __shared__ int warp_i[4];
+  __shared__ float warp_f[4];
+  const int lane = c & 31, warp = c >> 5;
+
+  const size_t at = static_cast<size_t>(t) * L.H + b * kBlock + c;
+  float v = __fmul_rn(__bfloat162float(hidden[at]),
+                      static_cast<float>(L.signs[b * kBlock + c]));
+  // Butterfly, half-widths 1..64: the member with the bit clear takes the sum,
+  // the member with the bit set takes (partner - own).
+#pragma unroll
+  for (int w = 1; w < 32; w <<= 1) {
+    const float o = __shfl_xor_sync(kFull, v, w);
+    v = (c & w) ? __fsub_rn(o, v) : __fadd_rn(v, o);
+  }
+#pragma unroll
+  for (int w = 32; w < kBlock; w <<= 1) {
+    sm[c] = v;
+    __syncthreads();
+    const float o = sm[c ^ w];
+    __syncthreads();
+    v = (c & w) ? __fsub_rn(o, v) : __fadd_rn(v, o);
+  }
+  v = __fmul_rn(v, 0.0883883461f);  // float(1 / sqrt(128))
+
+  // Rank by magnitude, ties to the lower coordinate.
+  const float a = fabsf(v);
+  sm[c] = a;
+  __syncthreads();
+  bool kept = true;
+  if (L.KEEP < kBlock) {
+    int rank = 0;
+#pragma unroll 8
+    for (int j = 0; j < kBlock; ++j) {
+      const float o = sm[j];
+      rank += (o > a) || (o == a && j < c);
+    }
+    kept = rank < L.KEEP;
+  }
+  // Compact kept coordinates in ascending coordinate order.
+  const unsigned ballot = __ballot_sync(kFull, kept);
+  if (lane == 0) warp_i[warp] = __popc(ballot);
+  // Block maximum magnitude (kept values are the largest, so this is theirs).
+  float m = a;
+#pragma unroll
+  for (int w = 16; w; w >>= 1) m = fmaxf(m, __shfl_xor_sync(kFull, m, w));
+  if (lane == 0) warp_f[warp] = m;
+  __syncthreads();
+  int position = __popc(ballot & ((1u << lane) - 1));
+  for (int w = 0; w < warp; ++w) position += warp_i[w];
+  m = fmaxf(fmaxf(warp_f[0], warp_f[1]), fmaxf(warp_f[2], warp_f[3]));
+  __syncthreads();
+
+  // Fixed point: q = rint(v * 2^(21 - e)), e = floor(log2 m) clamped to +-100.
+  int e = static_cast<int>((__float_as_uint(m) >> 23) & 0xff) - 127;
+  e = max(-100, min(100, e));
+  int q = 0;
+  float energy = 0.0f;
+  if (kept) {
+    const float scale = __uint_as_float(static_cast<uint32_t>(127 + kQuantBits - e) << 23);
+    q = (m > 0.0f) ? __float2int_rn(__fmul_rn(v, scale)) : 0;
+    q = max(-(1 << 22), min(1 << 22, q));
+    energy = __fmul_rn(v, v);
+    const size_t out = (static_cast<size_t>(t) * L.B + b) * L.KEEP + position;
+    ws.planes[out] = v;
+    ws.coordinates[out] = c;
+    ws.quantized[out] = q;
+  }
+  int qsum = q;
+#pragma unroll
+  for (int w = 16; w; w >>= 1) {
+    qsum += __shfl_xor_sync(kFull, qsum, w);
+    energy = __fadd_rn(energy, __shfl_xor_sync(kFull, energy, w));
+  }
+  if (lane == 0) {
+    warp_i[warp] = qsum;
+    warp_f[warp] = energy;
+  }
+  __syncthreads();
+  if (c == 0) {
+    const size_t row = static_cast<size_t>(t) * L.B + b;
+    ws.exponents[2 * row] = e;
+    ws.exponents[2 * row + 1] = warp_i[0] + warp_i[1] + warp_i[2] + warp_i[3];
+    ws.norms[row] = __fadd_rn(__fadd_rn(warp_f[0], warp_f[1]), __fadd_rn(warp_f[2], warp_f[3]));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// route: stable ascending sort of a token's experts
+// ---------------------------------------------------------------------------
+// grid (T), 32 threads.
+__global__ void __launch_bounds__(32) k_route(Layer L, Workspace ws, const void* ids,
+                                              int ids64, const void* weights, int wbf16) {
+  const int t = blockIdx.x, lane = threadIdx.x;
+  long long id = 0x7fffffffffffffffLL;
+  float w = 0.0f;
+  if (lane < L.K) {
+    const size_t at = static_cast<size_t>(t) * L.K + lane;
+    id = ids64 ? static_cast<const long long*>(ids)[at]
+               : static_cast<long long>(static_cast<const int32_t*>(ids)[at]);
+    w = wbf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(weights)[at])
+              : static_cast<const float*>(weights)[at];
+  }
+  int rank = 0;
+  for (int j = 0; j < L.K; ++j) {
+    const long long o = __shfl_sync(kFull, id, j);
+    rank += (o < id) || (o == id && j < lane);
+  }
+  if (lane < L.K) {
+    int local = -1;
+    if (L.expert_map) {
+      if (id >= 0 && id < L.global_experts) local = L.expert_map[id];
+    } else if (id >= 0 && id < L.E) {
+      local = static_cast<int>(id);
+    }
+    if (local >= L.E) local = -1;
+    const size_t out = static_cast<size_t>(t) * L.K + rank;
+    ws.ids[out] = local;
+    ws.weights[out] = w;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// screen: sketch GEMV + score
+// ---------------------------------------------------------------------------
+// grid (T*K pairs, S splits of the rotation blocks), W*CG threads.  Thread
+// (cg, wi) owns sketch word wi (16 rows) and the kept coordinates j = cg mod CG
+// of each block.  Integer partial dots are summed across coordinate groups in
+// shared memory; each thread then finishes 16/CG rows.
+template <int CG>
+__global__ void k_screen(Layer L, Workspace ws, const uint8_t* padding, int S) {
+  constexpr int RPT = kWordRows / CG;  // rows a thread finishes per block
+  constexpr int U = 8;                 // words in flight per thread
+  extern __shared__ int smem[];
+  const int rows = 2 * L.I, W = L.W, threads = W * CG;
+  int* sq = smem;              // [128] fixed-point values of the block
+  int* sc = sq + kBlock;       // [128] their coordinates
+  int* red = sc + kBlock;      // [CG * 16 * W] partial dots (CG > 1)
+  float* proj = reinterpret_cast<float*>(red + (CG > 1 ? CG * kWordRows * W : 0));  // [2I]
+  __shared__ int s_last;
+
+  const int pair = blockIdx.x, split = blockIdx.y;
+  const int t = pair / L.K, slot = pair - t * L.K;
+  const int tid = threadIdx.x, wi = tid % W, cg = tid / W;
+  const int e = ws.ids[pair];
+  const size_t cand0 = static_cast<size_t>(t) * L.N + static_cast<size_t>(slot) * L.I;
+  if ((padding && padding[t]) || e < 0) {
+    if (split == 0) {
+      for (int c = tid; c < L.I; c += threads) {
+        ws.scores[cand0 + c] = 0.0f;
+        ws.partial[static_cast<size_t>(t) * 2 * L.N + slot * L.I + c] = 0.0f;
+        ws.partial[static_cast<size_t>(t) * 2 * L.N + L.N + slot * L.I + c] = 0.0f;
+      }
+    }
+    return;
+  }
+  const int per = (L.B + S - 1) / S;
+  const int b0 = split * per, b1 = min(L.B, b0 + per);
+  float run[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) run[r] = 0.0f;
+  const int row0 = wi * kWordRows + cg * RPT;  // first row this thread finishes
+
+  for (int b = b0; b < b1; ++b) {
+    const size_t tb = static_cast<size_t>(t) * L.B + b;
+    __syncthreads();
+    for (int j = tid; j < L.KEEP; j += threads) {
+      sq[j] = ws.quantized[tb * L.KEEP + j];
+      sc[j] = ws.coordinates[tb * L.KEEP + j];
+    }
+    // Scales of the rows this thread finishes, fetched ahead of the dots.
+    float scale[RPT];
+    {
+      const __half* st = L.statistics +
+                         (static_cast<size_t>(e) * L.B + b) * 2 * rows + row0;
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) scale[r] = __half2float(st[r]);
+    }
+    const int be = ws.exponents[2 * tb], qsum = ws.exponents[2 * tb + 1];
+    __syncthreads();
+
+    int acc[kWordRows];
+#pragma unroll
+    for (int j = 0; j < kWordRows; ++j) acc[j] = 0;
+    const uint32_t* base =
+        L.sketch + (static_cast<size_t>(e) * L.H + static_cast<size_t>(b) * kBlock) * W + wi;
+    for (int j0 = cg; j0 < L.KEEP; j0 += CG * U) {
+      uint32_t word[U];
+      int q[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int j = j0 + u * CG;
+        if (j < L.KEEP) {
+          word[u] = load_stream4(base + static_cast<size_t>(sc[j]) * W);
+          q[u] = sq[j];
+        } else {
+          word[u] = 0;
+          q[u] = 0;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+#pragma unroll
+        for (int j = 0; j < kWordRows; ++j)
+          acc[j] += static_cast<int>((word[u] >> (2 * j)) & 3u) * q[u];
+      }
+    }
+    int dot[RPT];
+    if (CG > 1) {
+#pragma unroll
+      for (int j = 0; j < kWordRows; ++j) red[(cg * kWordRows + j) * W + wi] = acc[j];
+      __syncthreads();
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        int s = 0;
+#pragma unroll
+        for (int g = 0; g < CG; ++g) s += red[(g * kWordRows + cg * RPT + r) * W + wi];
+        dot[r] = s;
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) dot[r] = acc[r];
+    }
+    // code = trit + 1, so sum(trit * q) = sum(code * q) - sum(q).
+    const float unscale = __uint_as_float(static_cast<uint32_t>(127 + be - kQuantBits) << 23);
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const float d = __fmul_rn(__int2float_rn(dot[r] - qsum), unscale);
+      const float prod = __fmul_rn(scale[r], d);
+      if (S == 1) {
+        run[r] = __fadd_rn(run[r], prod);
+      } else {
+        ws.parts[(static_cast<size_t>(pair) * L.B + b) * rows + row0 + r] = prod;
+      }
+    }
+  }
+
+  if (S == 1) {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) proj[row0 + r] = run[r];
+  } else {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned old = atomicAdd(&ws.counters[pair], 1u);
+      s_last = (old == static_cast<unsigned>(S - 1));
+      if (s_last) ws.counters[pair] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // Sum the per-block products in block order.
+    for (int row = tid; row < rows; row += threads) {
+      float s = 0.0f;
+      const float* p = ws.parts + static_cast<size_t>(pair) * L.B * rows + row;
+      for (int b = 0; b < L.B; ++b) s = __fadd_rn(s, __ldcg(p + static_cast<size_t>(b) * rows));
+      proj[row] = s;
+    }
+  }
+  __syncthreads();
+  const float weight = ws.weights[pair];
+  for (int c = tid; c < L.I; c += threads) {
+    const float g = proj[c], u = proj[L.I + c];
+    ws.partial[static_cast<size_t>(t) * 2 * L.N + slot * L.I + c] = g;
+    ws.partial[static_cast<size_t>(t) * 2 * L.N + L.N + slot * L.I + c] = u;
+    const float norm = L.norms[static_cast<size_t>(e) * L.I + c];
+    ws.scores[cand0 + c] = point_score(g, u, norm, weight, L.activation);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// select: top-F per token, read-cost counters
+// ---------------------------------------------------------------------------
+constexpr int kSelectThreads = 1024;
+
+__device__ __forceinline__ int64_t sector_run(int64_t bytes) { return (bytes + 31) / 32 * 32; }
+
+// grid (T), 1024 threads, dynamic shared memory: N keys.
+__global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws,
+                                                           const uint8_t* padding) {
+  extern __shared__ uint32_t keys[];
+  __shared__ int hist[256];
+  __shared__ int warp_above[32], warp_ties[32];
+  __shared__ int s_digit, s_remaining;
+  __shared__ int s_starts[33];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int N = L.N, F = L.F, K = L.K, I = L.I;
+  int32_t* counts = ws.counts + static_cast<size_t>(t) * K;
+  int32_t* starts = ws.starts + static_cast<size_t>(t) * K;
+  int32_t* tile_starts = ws.tile_starts + static_cast<size_t>(t) * K;
+  if (padding && padding[t]) {
+    if (tid < K) counts[tid] = starts[tid] = tile_starts[tid] = 0;
+    return;
+  }
+  const bool screened = F < N;
+  uint32_t cut = 0;
+  int take_ties = 0;
+  if (screened) {
+    const float* score = ws.scores + static_cast<size_t>(t) * N;
+    for (int i = tid; i < N; i += kSelectThreads) keys[i] = __float_as_uint(score[i]);
+    // Radix search, most significant byte first, for the F-th largest key.
+    uint32_t prefix = 0, mask = 0;
+    int remaining = F;
+    for (int pass = 3; pass >= 0; --pass) {
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+      const int shift = 8 * pass;
+      for (int i = tid; i < N; i += kSelectThreads) {
+        const uint32_t k = keys[i];
+        if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1);
+      }
+      __syncthreads();
+      if (warp == 0) {
+        // Suffix counts over the 256 digits, 8 per lane, from the top digit down.
+        int mine[8], total = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          mine[j] = hist[255 - (lane * 8 + j)];
+          total += mine[j];
+        }
+        int before = total;  // inclusive scan over lanes
+#pragma unroll
+        for (int w = 1; w < 32; w <<= 1) {
+          const int o = __shfl_up_sync(kFull, before, w);
+          if (lane >= w) before += o;
+        }
+        before -= total;  // keys in strictly higher digits than this lane's
+        int found = -1, above = 0;
+        if (before < remaining && before + total >= remaining) {
+          int cum = before;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (found < 0 && cum + mine[j] >= remaining) {
+              found = 255 - (lane * 8 + j);
+              above = cum;
+            }
+            cum += mine[j];
+          }
+        }
+        if (found >= 0) {
+          s_digit = found;
+          s_remaining = remaining - above;
+        }
+      }
+      __syncthreads();
+      prefix |= static_cast<uint32_t>(s_digit) << shift;
+      mask |= 255u << shift;
+      remaining = s_remaining;
+      __syncthreads();
+    }
+    cut = prefix;
+    take_ties = remaining;
+  }
+
+  // Compaction in candidate order: thread owns a contiguous chunk.
+  const int chunk = (N + kSelectThreads - 1) / kSelectThreads;
+  const int begin = min(N, tid * chunk), end = min(N, begin + chunk);
+  int above = 0, ties = 0;
+  if (screened) {
+    for (int i = begin; i < end; ++i) {
+      const uint32_t k = keys[i];
+      above += k > cut;
+      ties += k == cut;
+    }
+  } else {
+    above = end - begin;
+  }
+  int above_scan = above, ties_scan = ties;
+#pragma unroll
+  for (int w = 1; w < 32; w <<= 1) {
+    const int oa = __shfl_up_sync(kFull, above_scan, w);
+    const int ot = __shfl_up_sync(kFull, ties_scan, w);
+    if (lane >= w) {
+      above_scan += oa;
+      ties_scan += ot;
+    }
+  }
+  if (lane == 31) {
+    warp_above[warp] = above_scan;
+    warp_ties[warp] = ties_scan;
+  }
+  __syncthreads();
+  int above_before = above_scan - above, ties_before = ties_scan - ties;
+  for (int w = 0; w < warp; ++w) {
+    above_before += warp_above[w];
+    ties_before += warp_ties[w];
+  }
+  int position = above_before + min(ties_before, take_ties);
+  uint8_t* selected = ws.selected + static_cast<size_t>(t) * N;
+  uint8_t* completed = ws.completed + static_cast<size_t>(t) * N;
+  int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * F;
+  const int32_t* route = ws.ids + static_cast<size_t>(t) * K;
+  for (int i = begin; i < end; ++i) {
+    bool keep = true;
+    if (screened) {
+      const uint32_t k = keys[i];
+      keep = k > cut;
+      if (k == cut) {
+        keep = ties_before < take_ties;
+        ++ties_before;
+      }
+    }
+    const int slot = i / I;
+    if (i - slot * I == 0) s_starts[slot] = position;
+    selected[i] = keep;
+    completed[i] = keep && route[slot] >= 0;
+    if (keep) list[position++] = i;
+  }
+  if (tid == 0) s_starts[K] = F;
+  __syncthreads();
+  if (warp == 0) {
+    const bool live = lane < K;
+    const int count = live ? s_starts[lane + 1] - s_starts[lane] : 0;
+    const bool local = live && route[lane] >= 0;
+    const int tiles = local ? (count + kDownTileRows - 1) / kDownTileRows : 0;
+    int scan = tiles;
+#pragma unroll
+    for (int w = 1; w < 32; w <<= 1) {
+      const int o = __shfl_up_sync(kFull, scan, w);
+      if (lane >= w) scan += o;
+    }
+    if (live) {
+      counts[lane] = count;
+      starts[lane] = s_starts[lane];
+      tile_starts[lane] = scan - tiles;
+    }
+    // Read-cost counters of this token (integers, so FP64 atomics are exact).
+    int local_slots = local, kept_local = local ? count : 0;
+#pragma unroll
+    for (int w = 16; w; w >>= 1) {
+      local_slots += __shfl_xor_sync(kFull, local_slots, w);
+      kept_local += __shfl_xor_sync(kFull, kept_local, w);
+    }
+    if (L.read_work && lane < CFM_READ_WORK_SLOTS) {
+      const bool ep = L.expert_map != nullptr;
+      const int64_t H = L.H, R = L.R;
+      const int64_t candidates = static_cast<int64_t>(local_slots) * I;
+      const int64_t native = 2 * (2 * kept_local * H + kept_local * H);
+      const int64_t dense_slot = 6 * static_cast<int64_t>(I) * H;
+      const int64_t reference = ep ? local_slots * dense_slot : K * dense_slot;
+      const int64_t recovery = 2 * R * (candidates - kept_local + (L.owner ? H : 0));
+      const bool residual = L.score != CFM_SCORE_POINT;
+      const int64_t code = 2 * ((I + 4) / 5), plane = 4 * I;
+      const int64_t sketch_exact =
+          screened ? local_slots * L.B * (L.KEEP * code + plane * (1 + residual)) : 0;
+      const int64_t sketch_sector =
+          screened ? local_slots * L.B *
+                         (L.KEEP * sector_run(code) + sector_run(plane) * (1 + residual))
+                   : 0;
+      // Bytes the screen kernel itself requests: 2-bit codes (I / 2 bytes per
+      // kept coordinate) and the FP16 scale plane.
+      const int64_t sketch_issued =
+          screened ? local_slots * L.B * (static_cast<int64_t>(L.KEEP) * (I / 2) + plane) : 0;
+      const int64_t selection =
+          screened ? ((L.geometry ? 12 : 4) * candidates) : 0;
+      int64_t value = 0;
+      switch (lane) {
+        case 0: case 6: value = native; break;
+        case 1: value = reference; break;
+        case 3: case 7: value = recovery; break;
+        case 4: case 9: value = selection; break;
+        case 5: value = sketch_exact; break;
+        case 10: value = screened ? H : 0; break;
+        case 11: value = sketch_issued; break;
+        case 17: value = sketch_sector; break;
+        case 12: value = 4 * H * kept_local; break;
+        case 13: value = 2 * H * kept_local; break;
+        case 14: value = 2 * R * (candidates - kept_local); break;
+        default: value = 0;
+      }
+      if (value) atomicAdd(L.read_work + lane, static_cast<double>(value));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// exact: gathered gate/up rows
+// ---------------------------------------------------------------------------
+constexpr int kExactWarps = 4;
+
+// grid (ceil(F / 4), T), 128 threads; one warp per kept candidate.
+__global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace ws,
+                                                            const __nv_bfloat16* hidden,
+                                                            const uint8_t* padding) {
+  extern __shared__ uint4 xs[];  // H bf16 values of the token
+  const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (padding && padding[t]) return;
+  const int chunks = L.H / 8;
+  const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
+  for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
+  __syncthreads();
+  const int index = blockIdx.x * kExactWarps + warp;
+  if (index >= L.F) return;
+  const int cid = ws.candidate_ids[static_cast<size_t>(t) * L.F + index];
+  if (cid < 0) return;
+  const int slot = cid / L.I, c = cid - slot * L.I;
+  const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
+  if (e < 0) return;
+  const uint4* gate = reinterpret_cast<const uint4*>(
+      L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
+  const uint4* up = gate + static_cast<size_t>(L.I) * L.H / 8;
+  float g = 0.0f, u = 0.0f;
+#pragma unroll 4
+  for (int i = lane; i < chunks; i += 32) {
+    const uint4 gw = load_stream16(gate + i), uw = load_stream16(up + i), xw = xs[i];
+    g = fmaf(bf16_lo(gw.x), bf16_lo(xw.x), g);
+    g = fmaf(bf16_hi(gw.x), bf16_hi(xw.x), g);
+    g = fmaf(bf16_lo(gw.y), bf16_lo(xw.y), g);
+    g = fmaf(bf16_hi(gw.y), bf16_hi(xw.y), g);
+    g = fmaf(bf16_lo(gw.z), bf16_lo(xw.z), g);
+    g = fmaf(bf16_hi(gw.z), bf16_hi(xw.z), g);
+    g = fmaf(bf16_lo(gw.w), bf16_lo(xw.w), g);
+    g = fmaf(bf16_hi(gw.w), bf16_hi(xw.w), g);
+    u = fmaf(bf16_lo(uw.x), bf16_lo(xw.x), u);
+    u = fmaf(bf16_hi(uw.x), bf16_hi(xw.x), u);
+    u = fmaf(bf16_lo(uw.y), bf16_lo(xw.y), u);
+    u = fmaf(bf16_hi(uw.y), bf16_hi(xw.y), u);
+    u = fmaf(bf16_lo(uw.z), bf16_lo(xw.z), u);
+    u = fmaf(bf16_hi(uw.z), bf16_hi(xw.z), u);
+    u = fmaf(bf16_lo(uw.w), bf16_lo(xw.w), u);
+    u = fmaf(bf16_hi(uw.w), bf16_hi(xw.w), u);
+  }
+#pragma unroll
+  for (int w = 16; w; w >>= 1) {
+    g += __shfl_xor_sync(kFull, g, w);
+    u += __shfl_xor_sync(kFull, u, w);
+  }
+  if (lane == 0) {
+    ws.activations[static_cast<size_t>(t) * L.N + cid] =
+        __float2bfloat16_rn(exact_feature(g, u, L.activation));
+    ws.exact[static_cast<size_t>(t) * 2 * L.F + index] = g;
+    ws.exact[static_cast<size_t>(t) * 2 * L.F + L.F + index] = u;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// down: gathered channel-major down rows
+// ---------------------------------------------------------------------------
+// grid (H / 128, down_tiles, T), 128 threads = 8 row groups x 16 lanes of 8
+// columns.  One CTA sums up to 128 kept rows of one expert over 128 columns.
+__global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8_t* padding) {
+  const int t = blockIdx.z, tile = blockIdx.y, tid = threadIdx.x;
+  if (padding && padding[t]) return;
+  const int32_t* tile_starts = ws.tile_starts + static_cast<size_t>(t) * L.K;
+  const int32_t* counts = ws.counts + static_cast<size_t>(t) * L.K;
+  int slot = -1, first = 0;
+  for (int s = 0; s < L.K; ++s) {
+    const int e = ws.ids[static_cast<size_t>(t) * L.K + s];
+    const int tiles = e >= 0 ? (counts[s] + kDownTileRows - 1) / kDownTileRows : 0;
+    if (tile >= tile_starts[s] && tile < tile_starts[s] + tiles) {
+      slot = s;
+      first = (tile - tile_starts[s]) * kDownTileRows;
+    }
+  }
+  if (slot < 0) return;
+  const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
+  const int rows = min(kDownTileRows, counts[slot] - first);
+  const int32_t* list =
+      ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[static_cast<size_t>(t) * L.K + slot] + first;
+  const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
+  const int group = tid >> 4, col = (tid & 15) * 8 + blockIdx.x * 128;
+  const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + col;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+#pragma unroll 4
+  for (int r = group; r < rows; r += 8) {
+    const int cid = list[r];
+    const int c = cid - slot * L.I;
+    const float a = __bfloat162float(act[cid]);
+    const uint4 w = load_stream16(base + static_cast<size_t>(c) * L.H);
+    acc[0] = fmaf(bf16_lo(w.x), a, acc[0]);
+    acc[1] = fmaf(bf16_hi(w.x), a, acc[1]);
+    acc[2] = fmaf(bf16_lo(w.y), a, acc[2]);
+    acc[3] = fmaf(bf16_hi(w.y), a, acc[3]);
+    acc[4] = fmaf(bf16_lo(w.z), a, acc[4]);
+    acc[5] = fmaf(bf16_hi(w.z), a, acc[5]);
+    acc[6] = fmaf(bf16_lo(w.w), a, acc[6]);
+    acc[7] = fmaf(bf16_hi(w.w), a, acc[7]);
+  }
+  __shared__ float red[8][128];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[group][(tid & 15) * 8 + j] = acc[j];
+  __syncthreads();
+  float s = 0.0f;
+#pragma unroll
+  for (int g = 0; g < 8; ++g) s += red[g][tid];
+  ws.down_parts[(static_cast<size_t>(t) * ws.down_tiles + tile) * L.H + blockIdx.x * 128 + tid] = s;
+}
+
+// ---------------------------------------------------------------------------
+// encode: recovery encoder over skipped channels, then the latent
+// ---------------------------------------------------------------------------
+// grid (encoder_tiles, T*K), 128 threads.  LPR = R / 8 lanes cover one encoder
+// row (16 bytes each); 128 / LPR row groups walk the tile's 64 channels.
+__global__ void __launch_bounds__(128) k_encode(Layer L, Workspace ws, const uint8_t* padding) {
+  __shared__ float red[128 * 8];
+  __shared__ int s_last;
+  const int tile = blockIdx.x, pair = blockIdx.y, tid = threadIdx.x;
+  const int t = pair / L.K, slot = pair - t * L.K;
+  const int R = L.R, lpr = R / 8, groups = 128 / lpr;
+  const int e = ws.ids[pair];
+  const bool dead = (padding && padding[t]) || e < 0;
+  const int group = tid / lpr, col = (tid - group * lpr) * 8;
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  if (!dead) {
+    const float* pg = ws.partial + static_cast<size_t>(t) * 2 * L.N + slot * L.I;
+    const float* pu = pg + L.N;
+    const uint8_t* sel = ws.selected + static_cast<size_t>(t) * L.N + slot * L.I;
+    const __nv_bfloat16* enc = L.encoder + static_cast<size_t>(e) * L.I * R + col;
+    const int c1 = min(L.I, (tile + 1) * kEncodeTileRows);
+#pragma unroll 2
+    for (int c = tile * kEncodeTileRows + group; c < c1; c += groups) {
+      if (sel[c]) continue;
+      const float p = sketch_feature(pg[c], pu[c], L.activation);
+      const uint4 w = *reinterpret_cast<const uint4*>(enc + static_cast<size_t>(c) * R);
+      acc[0] = fmaf(bf16_lo(w.x), p, acc[0]);
+      acc[1] = fmaf(bf16_hi(w.x), p, acc[1]);
+      acc[2] = fmaf(bf16_lo(w.y), p, acc[2]);
+      acc[3] = fmaf(bf16_hi(w.y), p, acc[3]);
+      acc[4] = fmaf(bf16_lo(w.z), p, acc[4]);
+      acc[5] = fmaf(bf16_hi(w.z), p, acc[5]);
+      acc[6] = fmaf(bf16_lo(w.w), p, acc[6]);
+      acc[7] = fmaf(bf16_hi(w.w), p, acc[7]);
+    }
+  }
+  // red[group][R]
+#pragma unroll
+  for (int j = 0; j < 8; ++j) red[group * R + col + j] = acc[j];
+  __syncthreads();
+  float* parts = ws.encoder_parts + (static_cast<size_t>(pair) * ws.encoder_tiles + tile) * R;
+  for (int r = tid; r < R; r += 128) {
+    float s = 0.0f;
+    for (int g = 0; g < groups; ++g) s += red[g * R + r];
+    parts[r] = s;
+  }
+  // Last CTA of the token mixes the latent.
+  __threadfence();
+  __syncthreads();
+  uint32_t* counter = ws.counters + 2 * static_cast<size_t>(ws.capacity) * L.K + t;
+  if (tid == 0) {
+    const unsigned total = static_cast<unsigned>(L.K * ws.encoder_tiles);
+    const unsigned old = atomicAdd(counter, 1u);
+    s_last = (old == total - 1);
+    if (s_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  for (int r = tid; r < R; r += 128) {
+    float latent = 0.0f;
+    for (int s = 0; s < L.K; ++s) {
+      const int pe = ws.ids[static_cast<size_t>(t) * L.K + s];
+      if (pe < 0 || (padding && padding[t])) continue;
+      const float* p = ws.encoder_parts +
+                       (static_cast<size_t>(t) * L.K + s) * ws.encoder_tiles * R + r;
+      float sum = 0.0f;
+      for (int j = 0; j < ws.encoder_tiles; ++j) sum += __ldcg(p + static_cast<size_t>(j) * R);
+      latent = fmaf(bf16_round(sum), ws.weights[static_cast<size_t>(t) * L.K + s], latent);
+    }
+    ws.latent[static_cast<size_t>(t) * R + r] = latent;
+  }
+}
+
+// grid (T), 128 threads: latent = 0 (no skipped channels, or no map).
+__global__ void k_zero_latent(Layer L, Workspace ws) {
+  for (int r = threadIdx.x; r < L.R; r += blockDim.x)
+    ws.latent[static_cast<size_t>(blockIdx.x) * L.R + r] = 0.0f;
+}
+
+// ---------------------------------------------------------------------------
+// output: router mix + decoder term
+// ---------------------------------------------------------------------------
+// grid (H / 128, T), 128 threads, one output column per thread.
+__global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uint8_t* padding,
+                                                __nv_bfloat16* out) {
+  __shared__ float latent[256];
+  const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
+  if (padding && padding[t]) {
+    out[static_cast<size_t>(t) * L.H + h] = __float2bfloat16_rn(0.0f);
+    return;
+  }
+  const bool recover = L.R > 0 && L.owner && L.decoder;
+  if (recover) {
+    for (int r = tid; r < L.R; r += 128)
+      latent[r] = bf16_round(ws.latent[static_cast<size_t>(t) * L.R + r]);
+    __syncthreads();
+  }
+  float routed = 0.0f;
+  for (int s = 0; s < L.K; ++s) {
+    const size_t pair = static_cast<size_t>(t) * L.K + s;
+    if (ws.ids[pair] < 0) continue;
+    const int tiles = (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows;
+    if (!tiles) continue;
+    const float* p = ws.down_parts +
+                     (static_cast<size_t>(t) * ws.down_tiles + ws.tile_starts[pair]) * L.H + h;
+    float sum = 0.0f;
+    for (int j = 0; j < tiles; ++j) sum += p[static_cast<size_t>(j) * L.H];
+    routed = fmaf(bf16_round(sum), ws.weights[pair], routed);
+  }
+  float correction = 0.0f;
+  if (recover) {
+    const uint4* row = reinterpret_cast<const uint4*>(L.decoder + static_cast<size_t>(h) * L.R);
+    float sum = 0.0f;
+    for (int i = 0; i < L.R / 8; ++i) {
+      const uint4 w = row[i];
+      const float* z = latent + i * 8;
+      sum = fmaf(bf16_lo(w.x), z[0], sum);
+      sum = fmaf(bf16_hi(w.x), z[1], sum);
+      sum = fmaf(bf16_lo(w.y), z[2], sum);
+      sum = fmaf(bf16_hi(w.y), z[3], sum);
+      sum = fmaf(bf16_lo(w.z), z[4], sum);
+      sum = fmaf(bf16_hi(w.z), z[5], sum);
+      sum = fmaf(bf16_lo(w.w), z[6], sum);
+      sum = fmaf(bf16_hi(w.w), z[7], sum);
+    }
+    correction = bf16_round(sum);
+  }
+  out[static_cast<size_t>(t) * L.H + h] = __float2bfloat16_rn(routed + correction);
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+struct Bound {
+  Layer L;
+  Workspace ws;
+  cudaStream_t stream;
+  int T;
+  const uint8_t* padding;
+};
+
+static int bind_call(const cfm_layer* layer, void* workspace, int32_t capacity,
+                     const cfm_call* call, void* stream, Bound* b) {
+  if (!layer || !workspace || !call) return CFM_E_NULL;
+  cfm_workspace_layout layout;
+  const int rc = make_layout(layer, capacity, &layout);
+  if (rc) return rc;
+  if (call->tokens < 1 || call->tokens > capacity) return CFM_E_CAPACITY;
+  if (layer->experts < 1 || !layer->gate_up || !layer->down) return CFM_E_NULL;
+  if (layer->activation != CFM_ACT_SILU && layer->activation != CFM_ACT_GELU_TANH)
+    return CFM_E_UNSUPPORTED;
+  if (layer->score != CFM_SCORE_POINT) return CFM_E_UNSUPPORTED;
+  const bool screened = layer->final_count < layer->top_k * layer->width;
+  if (screened && (!layer->sketch || !layer->statistics || !layer->norms || !layer->signs))
+    return CFM_E_NULL;
+  if (layer->rank && (!layer->encoder || !layer->decoder)) return CFM_E_NULL;
+  b->L = device_layer(layer);
+  b->ws = bind(layout, workspace, capacity);
+  b->stream = static_cast<cudaStream_t>(stream);
+  b->T = call->tokens;
+  b->padding = call->padding;
+  return 0;
+}
+
+static int launched() {
+  const cudaError_t err = cudaGetLastError();
+  return err == cudaSuccess ? 0 : static_cast<int>(err);
+}
+
+static int run_prepare(const Bound& b, const cfm_call* call) {
+  if (b.L.F >= b.L.N) return 0;
+  if (!call->hidden) return CFM_E_NULL;
+  k_prepare<<<dim3(b.T, b.L.B), kBlock, 0, b.stream>>>(
+      b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden), b.padding);
+  return launched();
+}
+
+static int run_route(const Bound& b, const cfm_call* call) {
+  if (!call->ids || !call->weights) return CFM_E_NULL;
+  k_route<<<b.T, 32, 0, b.stream>>>(b.L, b.ws, call->ids, call->ids_are_int64, call->weights,
+                                    call->weights_are_bf16);
+  return launched();
+}
+
+template <int CG>
+static int launch_screen(const Bound& b, int S) {
+  const int threads = b.L.W * CG;
+  const size_t smem = sizeof(int) * (2 * kBlock + (CG > 1 ? CG * kWordRows * b.L.W : 0)) +
+                      sizeof(float) * 2 * b.L.I;
+  if (smem > 48 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(
+        k_screen<CG>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  k_screen<CG><<<dim3(b.T * b.L.K, S), threads, smem, b.stream>>>(b.L, b.ws, b.padding, S);
+  return launched();
+}
+
+static int run_screen(const Bound& b) {
+  if (b.L.F >= b.L.N) return 0;
+  // Split the rotation blocks across CTAs while the batch is too small to fill
+  // the 148 SMs; large batches keep each pair's blocks in one CTA.
+  const int pairs = b.T * b.L.K;
+  int S = 1;
+  if (b.T <= b.ws.parts_tokens) {
+    while (S < b.L.B && pairs * S < 2 * 148) S *= 2;
+    if (S > b.L.B) S = b.L.B;
+  }
+  // Coordinate groups: as many as keep the CTA within 1024 threads, at most 4.
+  int cg = 4;
+  while (cg > 1 && b.L.W * cg > 1024) cg >>= 1;
+  if (b.L.W > 1024) return CFM_E_SHAPE;
+  switch (cg) {
+    case 4: return launch_screen<4>(b, S);
+    case 2: return launch_screen<2>(b, S);
+    default: return launch_screen<1>(b, S);
+  }
+}
+
+static int run_select(const Bound& b) {
+  const size_t smem = sizeof(uint32_t) * b.L.N;
+  if (smem > 48 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(
+        k_select, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  k_select<<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding);
+  return launched();
+}
+
+static int run_exact(const Bound& b, const cfm_call* call) {
+  if (!call->hidden) return CFM_E_NULL;
+  const size_t smem = static_cast<size_t>(b.L.H) * 2;
+  if (smem > 48 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(
+        k_exact, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  k_exact<<<dim3((b.L.F + kExactWarps - 1) / kExactWarps, b.T), kExactWarps * 32, smem,
+            b.stream>>>(b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden), b.padding);
+  return launched();
+}
+
+static int run_down(const Bound& b) {
+  k_down<<<dim3(b.L.H / 128, b.ws.down_tiles, b.T), 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+  return launched();
+}
+
+static int run_encode(const Bound& b) {
+  if (b.L.R == 0) return 0;
+  if (b.L.F >= b.L.N) {
+    k_zero_latent<<<b.T, 128, 0, b.stream>>>(b.L, b.ws);
+    return launched();
+  }
+  k_encode<<<dim3(b.ws.encoder_tiles, b.T * b.L.K), 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+  return launched();
+}
+
+static int run_output(const Bound& b, const cfm_call* call) {
+  if (!call->out) return CFM_E_NULL;
+  k_output<<<dim3(b.L.H / 128, b.T), 128, 0, b.stream>>>(
+      b.L, b.ws, b.padding, static_cast<__nv_bfloat16*>(call->out));
+  return launched();
+}
+
+}  // namespace cfm
+
+// ---------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------
+using namespace cfm;
+
+extern "C" {
+
+int cfm_abi_version(void) { return CFM_ABI_VERSION; }
+
+const char* cfm_error_string(int code) {
+  switch (code) {
+    case 0: return "success";
+    case CFM_E_NULL: return "a required pointer is NULL";
+    case CFM_E_SHAPE: return "a dimension violates the layer contract";
+    case CFM_E_CAPACITY: return "token count outside the workspace capacity";
+    case CFM_E_UNSUPPORTED: return "option not supported by this build";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
+  }
+}
+
+int cfm_workspace_layout_for(const cfm_layer* layer, int32_t capacity,
+                             cfm_workspace_layout* layout) {
+  return make_layout(layer, capacity, layout);
+}
+
+#define CFM_STAGE(name, body)                                                      \
+  int name(const cfm_layer* layer, void* workspace, int32_t capacity,             \
+           const cfm_call* call, void* stream) {                                   \
+    Bound b;                                                                       \
+    const int rc = bind_call(layer, workspace, capacity, call, stream, &b);        \
+    if (rc) return rc;                                                             \
+    body                                                                           \
+  }
+
+CFM_STAGE(cfm_prepare_input, return run_prepare(b, call);)
+CFM_STAGE(cfm_route, return run_route(b, call);)
+CFM_STAGE(cfm_screen, return run_screen(b);)
+CFM_STAGE(cfm_select, return run_select(b);)
+CFM_STAGE(cfm_exact, return run_exact(b, call);)
+CFM_STAGE(cfm_down, return run_down(b);)
+CFM_STAGE(cfm_encode, return run_encode(b);)
+CFM_STAGE(cfm_output, return run_output(b, call);)
+
+int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity,
+                       const cfm_call* call, void* stream) {
+  Bound b;
+  int rc = bind_call(layer, workspace, capacity, call, stream, &b);
+  if (rc) return rc;
+  if (!call->input_prepared && (rc = run_prepare(b, call))) return rc;
+  if ((rc = run_route(b, call))) return rc;
+  if ((rc = run_screen(b))) return rc;
+  if ((rc = run_select(b))) return rc;
+  if ((rc = run_exact(b, call))) return rc;
+  if ((rc = run_down(b))) return rc;
+  if ((rc = run_encode(b))) return rc;
+  return run_output(b, call);
+}
+
+}  // extern "C"

@@ -1,0 +1,195 @@
+/*
+ * C ABI of the B200 (sm_100a) sparse MoE decode reader.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream,
+ * enqueues work on that stream and returns without synchronising.  Nothing
+ * here allocates device memory: the caller owns weights, sketch, workspace and
+ * outputs.  Return value 0 is success, a negative value is one of the
+ * CFM_E_* argument errors (nothing was launched), a positive value is a
+ * cudaError_t from a launch.  The host-side Python operator
+ * (`ProgressiveReader`) is the only intended caller; it raises ValueError
+ * before calling for every contract violation the reference rejects.
+ *
+ * The functions replace, stage by stage, the Triton launches of the
+ * reference's `calibration_free_moe/reader/progressive.py`; each declaration
+ * cites the reference code it stands for.
+ *
+ * Symbols: H hidden size, I channels per expert, E local experts, K experts
+ * per token, N = K * I candidates per token, F channels kept per token,
+ * R recovery rank, B = H / 128 rotation blocks, KEEP kept rotated coordinates
+ * per block, T tokens in a call, C workspace capacity in tokens.
+ */
+#ifndef CFM_B200_H
+#define CFM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CFM_ABI_VERSION 1
+
+/* argument errors */
+#define CFM_E_NULL -1       /* a required pointer is NULL                      */
+#define CFM_E_SHAPE -2      /* a dimension violates the layer contract          */
+#define CFM_E_CAPACITY -3   /* T outside [1, C] or workspace too small          */
+#define CFM_E_UNSUPPORTED -4 /* option not built (e.g. an unknown score code)   */
+
+#define CFM_ACT_SILU 0
+#define CFM_ACT_GELU_TANH 1
+#define CFM_SCORE_POINT 0
+#define CFM_SCORE_RECOVERY_AWARE 1
+#define CFM_READ_WORK_SLOTS 20
+
+/* One MoE layer: dimensions and resident tensors.  Mirrors the state
+ * `ProgressiveReader.__init__` prepares (reference progressive.py:3133-3515). */
+typedef struct cfm_layer {
+  int32_t hidden;         /* H, multiple of 128                                */
+  int32_t width;          /* I, multiple of 16                                 */
+  int32_t experts;        /* E, experts resident on this device                */
+  int32_t top_k;          /* K <= 32                                           */
+  int32_t final_count;    /* F, 1 <= F <= N; F == N disables the screen        */
+  int32_t keep;           /* KEEP in [1, 128]                                  */
+  int32_t rank;           /* R, 0 = no recovery map; else multiple of 8, <= 256 */
+  int32_t activation;     /* CFM_ACT_*                                         */
+  int32_t score;          /* CFM_SCORE_*                                       */
+  int32_t global_experts; /* length of expert_map, 0 when expert_map is NULL   */
+  int32_t recovery_owner; /* 1 if this rank adds the decoder term              */
+  int32_t reserved;
+  const void* gate_up;       /* bf16 [E, 2I, H] contiguous                      */
+  const void* down;          /* bf16 physical [E, I, H] (channel-major)         */
+  const uint32_t* sketch;    /* kernel layout [E, H, 2I/16], 2 bits per trit    */
+  const void* statistics;    /* fp16 physical [E, B, 2, 2I]: scale, variance    */
+  const float* norms;        /* f32 [E, I], down-column norms                   */
+  const float* geometry;     /* f32 [E, I, 2] or NULL (recovery-aware score)    */
+  const void* encoder;       /* bf16 [E, I, R] or NULL                          */
+  const void* decoder;       /* bf16 [H, R] or NULL                             */
+  const int8_t* signs;       /* int8 [H], +-1                                   */
+  const int32_t* expert_map; /* i32 [global_experts] global->local, -1 remote   */
+  double* read_work;         /* f64 [20] read-cost counters, accumulated        */
+} cfm_layer;
+
+/* One call.  Mirrors the arguments of `ProgressiveReader.__call__`
+ * (reference progressive.py:3875-3926). */
+typedef struct cfm_call {
+  int32_t tokens;         /* T                                                 */
+  int32_t ids_are_int64;  /* ids element type: 0 int32, 1 int64                */
+  int32_t weights_are_bf16; /* router weight type: 0 float32, 1 bfloat16       */
+  int32_t input_prepared; /* 1: cfm_prepare_input already ran for these rows   */
+  const void* hidden;     /* bf16 [T, H]                                       */
+  const void* ids;        /* [T, K] router expert ids (global ids under EP)    */
+  const void* weights;    /* [T, K] router weights                             */
+  const uint8_t* padding; /* bool [T] or NULL; 1 marks a padding row           */
+  void* out;              /* bf16 [T, H]                                       */
+} cfm_call;
+
+/* Byte offsets of every scratch array inside one workspace allocation of
+ * `bytes` bytes (256-byte aligned).  Mirrors the tensors of `ReaderWorkspace`
+ * (reference progressive.py:2868-3121); names follow the reference where the
+ * array has a counterpart. */
+typedef struct cfm_workspace_layout {
+  int64_t bytes;
+  int64_t ids;            /* i32 [C, K]  experts sorted ascending, local ids    */
+  int64_t weights;        /* f32 [C, K]  router weights in the same order       */
+  int64_t norms;          /* f32 [C, B]  energy of the kept rotated coordinates */
+  int64_t planes;         /* f32 [C, B, KEEP] kept rotated values               */
+  int64_t coordinates;    /* i32 [C, B, KEEP] their coordinates, ascending      */
+  int64_t quantized;      /* i32 [C, B, KEEP] fixed-point kept values           */
+  int64_t exponents;      /* i32 [C, B, 2] fixed-point exponent, sum of values  */
+  int64_t parts;          /* f32 [PARTS_TOKENS * K, B, 2I] per-block products   */
+  int64_t counters;       /* u32 [2 * C * K + 2 * C] arrival counters (zero)    */
+  int64_t partial;        /* f32 [C, 2, N] sketch projections (gate, up)        */
+  int64_t scores;         /* f32 [C, N]                                         */
+  int64_t selected;       /* u8  [C, N]                                         */
+  int64_t completed;      /* u8  [C, N]                                         */
+  int64_t candidate_ids;  /* i32 [C, F] kept candidates, ascending              */
+  int64_t counts;         /* i32 [C, K]                                         */
+  int64_t starts;         /* i32 [C, K]                                         */
+  int64_t tile_starts;    /* i32 [C, K]                                         */
+  int64_t activations;    /* bf16 [C, N] exact phi(g) u of kept candidates      */
+  int64_t exact;          /* f32 [C, 2, F] exact gate and up projections        */
+  int64_t down_parts;     /* f32 [C, down_tiles, H]                             */
+  int64_t encoder_parts;  /* f32 [C, K, encoder_tiles, R]                       */
+  int64_t latent;         /* f32 [C, R]                                         */
+  int64_t status;         /* i32 [4] device-side error flags (zero = healthy)   */
+  int32_t parts_tokens;   /* tokens the split screen can serve                  */
+  int32_t down_tiles;     /* ceil(F / 128) + K - 1                              */
+  int32_t encoder_tiles;  /* ceil(I / 64)                                       */
+  int32_t reserved;
+} cfm_workspace_layout;
+
+/* ABI version of the loaded library (== CFM_ABI_VERSION of this header). */
+int cfm_abi_version(void);
+
+/* Text for a return code of this library. */
+const char* cfm_error_string(int code);
+
+/* Fill `layout` for a layer's dimensions and a capacity of C tokens.  Reads
+ * only hidden/width/top_k/final_count/keep/rank of `layer`.
+ * Replaces: ReaderWorkspace.__init__ sizing (progressive.py:2885-3121). */
+int cfm_workspace_layout_for(const cfm_layer* layer, int32_t capacity,
+                             cfm_workspace_layout* layout);
+
+/* Input rotation: BF16 rows -> sign flip, 128-point Hadamard butterfly, keep
+ * the KEEP largest |v| per block (ties to the lower coordinate), fixed-point
+ * copy of the kept values.  Replaces: _prepare_input / _rotate_sketch_block
+ * (progressive.py:304-346,389-453), launched by prepare_input (:3829-3873). */
+int cfm_prepare_input(const cfm_layer* layer, void* workspace, int32_t capacity,
+                      const cfm_call* call, void* stream);
+
+/* Route: per token, sort the K expert ids ascending (stable), carry the
+ * weights, map global to local ids.  Replaces: _prepare / _route
+ * (progressive.py:143-239,349-386). */
+int cfm_route(const cfm_layer* layer, void* workspace, int32_t capacity,
+              const cfm_call* call, void* stream);
+
+/* Screen: sketch GEMV of every candidate channel of every routed local expert
+ * and the selection score.  Writes `partial` and `scores`; rows of remote or
+ * padded slots are zero.  Replaces: _sketch_screen and its helpers
+ * (progressive.py:478-1066), _screen_score (:1274-1353). */
+int cfm_screen(const cfm_layer* layer, void* workspace, int32_t capacity,
+               const cfm_call* call, void* stream);
+
+/* Select: per token the F best scores, ties to the lower candidate index;
+ * writes selected, candidate_ids, counts, starts, tile_starts and adds the
+ * call's read-cost counters.  Replaces: _select (progressive.py:1584-1775),
+ * _account_fixed (:242-276), _count_reads (:2114-2317). */
+int cfm_select(const cfm_layer* layer, void* workspace, int32_t capacity,
+               const cfm_call* call, void* stream);
+
+/* Exact gate/up: native BF16 rows of the kept candidates against the input,
+ * FP32 accumulation, phi(g) u with the reference's BF16 rounding points.
+ * Replaces: _acquire with END == H (progressive.py:1372-1581). */
+int cfm_exact(const cfm_layer* layer, void* workspace, int32_t capacity,
+              const cfm_call* call, void* stream);
+
+/* Down: channel-major down rows of the kept candidates, weighted by their
+ * activations, FP32 partial sums per tile of 128 kept rows.
+ * Replaces: _down (progressive.py:1778-1856). */
+int cfm_down(const cfm_layer* layer, void* workspace, int32_t capacity,
+             const cfm_call* call, void* stream);
+
+/* Recovery encode: sketch features of the skipped channels through the
+ * encoder rows, then the router-weighted latent.  Replaces: _encode and
+ * _latent (progressive.py:1859-2016). */
+int cfm_encode(const cfm_layer* layer, void* workspace, int32_t capacity,
+               const cfm_call* call, void* stream);
+
+/* Output: mix the per-expert down sums by router weight, add the decoder
+ * term, store BF16.  Replaces: _output (progressive.py:2019-2111). */
+int cfm_output(const cfm_layer* layer, void* workspace, int32_t capacity,
+               const cfm_call* call, void* stream);
+
+/* The whole layer on one stream: prepare (unless input_prepared), route,
+ * screen, select, exact, down, encode, output.  Single-device readers only;
+ * expert-parallel readers call the stages with their collectives between.
+ * Replaces: ProgressiveReader.__call__ (progressive.py:3875-4472). */
+int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity,
+                       const cfm_call* call, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CFM_B200_H */
