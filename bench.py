@@ -1,0 +1,462 @@
+"""Benchmark of the sparse MoE decode reader: decode tokens/s on a Qwen3-30B-A3B-shaped layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--tokens T] [--layers L] [--config NAME]
+
+A step is one call of the reader on one batch of T decode tokens of one MoE
+layer.  Steps cycle over L independent layers (own weights, own inputs) so that
+consecutive steps touch different memory and the bytes come from HBM, not L2.
+Inputs are synthetic (`cfm_b200.synthetic`), drawn on the device.
+
+The JSON line printed by rank 0 reports whole-job tokens/s with inputs resident
+(`value`), the same through the public operator with host buffers and copies in
+the timed region (`e2e`), the dominant kernel's HBM roofline fraction measured
+with CUDA events (`roofline`), the whole layer's (`layer_roofline`), and the CPU
+oracle timed on the host cores (`cpu_baseline`).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+import cfm_b200  # noqa: E402,F401
+from cfm_b200 import synthetic  # noqa: E402
+from cfm_b200.reader.budget import compile_budget  # noqa: E402
+
+METRIC = "sparse-MoE decode tok/s (Qwen3-30B-A3B shape)"
+UNIT = "tokens/s"
+STAGES = ("cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_select", "cfm_exact",
+          "cfm_down", "cfm_encode", "cfm_output")
+KERNEL_OF_STAGE = {
+    "cfm_prepare_input": "k_prepare", "cfm_route": "k_route", "cfm_screen": "k_screen",
+    "cfm_select": "k_select", "cfm_exact": "k_exact", "cfm_down": "k_down",
+    "cfm_encode": "k_encode", "cfm_output": "k_output",
+}
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# workload
+# ---------------------------------------------------------------------------
+def device_layer(shape: synthetic.LayerShape, seed: int, device: torch.device):
+    """Random BF16 weights of one layer, drawn on the device."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    e, h, i, r = shape.experts, shape.hidden, shape.width, shape.rank
+    gate_up = torch.empty(e, 2 * i, h, device=device, dtype=torch.bfloat16)
+    down = torch.empty(e, i, h, device=device, dtype=torch.bfloat16)  # physical channel-major
+    for expert in range(e):  # one expert at a time keeps the FP32 temporaries small
+        gate_up[expert] = (torch.randn(2 * i, h, device=device, generator=g) * shape.sigma).bfloat16()
+        down[expert] = (torch.randn(i, h, device=device, generator=g) * shape.sigma).bfloat16()
+    router = (torch.randn(e, h, device=device, generator=g) * shape.sigma).bfloat16()
+    decoder = torch.linalg.qr(torch.randn(h, r, device=device, generator=g)).Q.bfloat16()
+    encoder = torch.stack(
+        [torch.linalg.qr(torch.randn(i, r, device=device, generator=g)).Q.T for _ in range(e)]
+    ).bfloat16()
+    return gate_up, down.transpose(1, 2), router, decoder, encoder, g
+
+
+def device_batch(shape, router, tokens, generator, device):
+    h, k = shape.hidden, shape.top_k
+    x = torch.randn(tokens, h, device=device, generator=generator)
+    if shape.input_kind == "outliers":
+        count = -(-h // 100)
+        dims = torch.randperm(h, device=device, generator=generator)[:count]
+        x[:, dims] *= 20.0
+    elif shape.input_kind == "student_t":
+        chi = torch.randn(tokens, h, 3, device=device, generator=generator).square().sum(-1)
+        x = x / (chi / 3).sqrt() / 3.0**0.5
+    hidden = x.bfloat16()
+    logits = hidden.float() @ router.float().T
+    if shape.router_bias:
+        logits = logits + torch.randn(router.shape[0], device=device, generator=generator)
+    weights, ids = torch.softmax(logits, -1, dtype=torch.float32).topk(k, -1)
+    if shape.renormalize:
+        weights = weights / weights.sum(-1, keepdim=True)
+    return hidden, ids.int().contiguous(), weights.float().contiguous()
+
+
+def algorithmic_bytes(reader, tokens: int) -> dict[str, float]:
+    """Distinct bytes one call must bring from HBM, from the realised routing and selection.
+
+    Per routed local expert: the code runs of the union of its tokens' kept
+    coordinates (kernel layout, I/2 bytes per coordinate), its FP16 scale planes
+    and FP32 norms; gate, up and down rows of the union of kept channels; encoder
+    rows of the union of skipped channels.  Plus the decoder, the signs and the
+    tokens' inputs, outputs and routes.
+    """
+    p = reader.plan
+    h, i, k, r = p.hidden_size, p.expert_width, p.top_k, reader.rank
+    blocks = h // 128
+    e = reader.native_gu.shape[0]
+    ids = reader.ids[:tokens].long()  # [T, K] sorted local ids
+    selected = reader.selected[:tokens].reshape(tokens, k, i)
+    valid = ids >= 0
+    flat = ids.clamp_min(0).reshape(-1)
+    kept_union = torch.zeros(e, i, dtype=torch.bool, device=ids.device)
+    kept_union.index_put_((flat,), selected.reshape(-1, i) & valid.reshape(-1, 1), accumulate=True)
+    skipped_union = torch.zeros_like(kept_union)
+    skipped_union.index_put_((flat,), ~selected.reshape(-1, i) & valid.reshape(-1, 1), accumulate=True)
+    routed = torch.zeros(e, dtype=torch.bool, device=ids.device)
+    routed[flat[valid.reshape(-1)]] = True
+    coordinates = reader.sketch_coordinates[:tokens].long()  # [T, B, KEEP]
+    support = torch.zeros(tokens, blocks, 128, dtype=torch.bool, device=ids.device)
+    support.scatter_(-1, coordinates, True)
+    support = support.reshape(tokens, h)
+    coordinate_union = torch.zeros(e, h, dtype=torch.bool, device=ids.device)
+    coordinate_union.index_put_(
+        (flat,), support[:, None, :].expand(tokens, k, h).reshape(-1, h) & valid.reshape(-1, 1),
+        accumulate=True,
+    )
+    experts = int(routed.sum())
+    screen = int(coordinate_union.sum()) * (i // 2) + experts * (blocks * 2 * (2 * i) + 4 * i)
+    kept = int(kept_union.sum())
+    exact = kept * 2 * 2 * h
+    down = kept * 2 * h
+    encode = int(skipped_union.sum()) * 2 * r
+    fixed = 2 * h * r + h + tokens * (4 * h + 8 * k)
+    return {
+        "k_screen": float(screen), "k_exact": float(exact + tokens * 2 * h),
+        "k_down": float(down), "k_encode": float(encode), "k_output": float(2 * h * r),
+        "total": float(screen + exact + down + encode + fixed),
+    }
+
+
+class ClockSampler:
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int) -> None:
+        self.process = None
+        try:
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
+            )
+        except OSError:
+            pass
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.process.terminate()
+        try:
+            text, _ = self.process.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+            text = ""
+        clocks, maxima, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in text.strip().splitlines():
+            fields = [f.strip() for f in line.split(",")]
+            if len(fields) < 7:
+                continue
+            try:
+                clocks.append(float(fields[0]))
+                maxima.append(float(fields[1]))
+            except ValueError:
+                continue
+            for name, field in zip(names, fields[3:7]):
+                if field.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        return {
+            "sm_mhz": clocks[len(clocks) // 2] if clocks else None,
+            "sm_max_mhz": max(maxima) if maxima else None,
+            "samples": len(clocks),
+            "reasons": sorted(reasons),
+        }
+
+
+# ---------------------------------------------------------------------------
+# arms
+# ---------------------------------------------------------------------------
+def cpu_oracle_rate(shape, plan, tokens: int, seconds: float = 10.0) -> dict:
+    """Time the CPU oracle (a port of the reference's PyTorch reader) on the host cores."""
+    from cfm_b200.reader.progressive import channel_major_down
+    from cfm_b200.reader.sketch import block_hadamard_signs, build_sketch
+    from oracle import reader_oracle
+
+    layer, g = synthetic.make_layer(shape, 0)
+    hidden, ids, weights = synthetic.make_batch(layer, tokens, g)
+    signs = block_hadamard_signs(shape.hidden, "cpu")
+    codes, statistics = build_sketch(layer.gate_up, signs)
+    down = channel_major_down(layer.down)
+    norms = down.float().square().sum(1).sqrt()
+    arguments = dict(
+        plan=plan, gate_up=layer.gate_up, down=down, codes=codes, statistics=statistics,
+        signs=signs, hidden=hidden, ids=ids, weights=weights, encoder=layer.encoder,
+        decoder=layer.decoder, norms=norms,
+    )
+    threads = reader_oracle.forward(**{**arguments, "hidden": hidden[:1], "ids": ids[:1],
+                                       "weights": weights[:1]})["threads"]
+    done, elapsed, cores = 0, 0.0, 1
+    while elapsed < seconds and done < 8 * tokens:
+        start = time.perf_counter()
+        cores = reader_oracle.forward(**arguments)["threads"]
+        elapsed += time.perf_counter() - start
+        done += tokens
+    del threads
+    return {
+        "value": done / elapsed, "unit": UNIT, "cores": cores, "kind": "port",
+        "sample": f"{done} tokens of the {shape.name} layer in batches of {tokens} "
+                  f"({elapsed:.1f} s; sketch construction excluded)",
+    }
+
+
+def run_reference(args, shape, plan) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    tokens = min(args.tokens, 64)
+    from cfm_b200.reader.progressive import channel_major_down
+    from cfm_b200.reader.sketch import block_hadamard_signs, build_sketch
+    from oracle import reader_oracle
+
+    layer, g = synthetic.make_layer(shape, 0)
+    hidden, ids, weights = synthetic.make_batch(layer, tokens, g)
+    signs = block_hadamard_signs(shape.hidden, "cpu")
+    codes, statistics = build_sketch(layer.gate_up, signs)
+    down = channel_major_down(layer.down)
+    arguments = dict(
+        plan=plan, gate_up=layer.gate_up, down=down, codes=codes, statistics=statistics,
+        signs=signs, hidden=hidden, ids=ids, weights=weights, encoder=layer.encoder,
+        decoder=layer.decoder, norms=down.float().square().sum(1).sqrt(),
+    )
+    cores = 1
+    for _ in range(args.warmup):
+        cores = reader_oracle.forward(**arguments)["threads"]
+    start = time.perf_counter()
+    for _ in range(args.steps):
+        reader_oracle.forward(**arguments)
+    elapsed = time.perf_counter() - start
+    value = tokens * args.steps / elapsed
+    sample = f"{tokens} tokens per step of the {shape.name} layer, CPU port of the reference reader"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * elapsed / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(shape, plan, tokens, 1, args.gpus),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(shape, plan, tokens, layers, gpus) -> dict:
+    return {
+        "workload": f"{shape.name}-shaped MoE layer, decode batch {tokens}",
+        "hidden": shape.hidden, "experts": shape.experts, "expert_width": shape.width,
+        "top_k": shape.top_k, "recovery_rank": shape.rank, "kept_channels": plan.final_count,
+        "screen_coordinates": plan.screen_coordinates, "selection_score": "point",
+        "tokens_per_step": tokens, "layers_cycled": layers,
+        "l2": f"steps cycle over {layers} layers with distinct weights and inputs",
+        "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas",
+    }
+
+
+def run_ours(args, shape, plan) -> None:
+    import ctypes
+
+    from cfm_b200 import _native
+    from cfm_b200.reader.progressive import ProgressiveReader, ReaderWorkspace
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    distributed = world > 1
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if distributed:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=device)
+    tokens, layers = args.tokens, args.layers
+    workspace = ReaderWorkspace(plan, shape.experts, shape.rank, tokens, device)
+    readers, batches = [], []
+    for index in range(layers):
+        gate_up, down, router, decoder, encoder, g = device_layer(shape, 1000 * rank + index, device)
+        readers.append(ProgressiveReader(
+            gate_up, down, encoder, decoder, plan, tokens, workspace=workspace,
+            selection_score="point", retain_reference_sketch=False,
+        ))
+        batches.append(device_batch(shape, router, tokens, g, device))
+        del router
+    outs = [torch.empty_like(b[0]) for b in batches]
+    stream = torch.cuda.Stream(device)
+
+    def step(index: int) -> None:
+        hidden, ids, weights = batches[index]
+        readers[index](hidden, ids, weights, None, outs[index])
+
+    with torch.cuda.stream(stream):
+        for index in range(layers):
+            step(index)
+        stream.synchronize()
+        graphs = []
+        for index in range(layers):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step(index)
+            graphs.append(graph)
+
+        def barrier() -> None:
+            if distributed:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        # ---- resident-input throughput ---------------------------------
+        for i in range(args.warmup):
+            graphs[i % layers].replay()
+        barrier()
+        sampler = ClockSampler(local) if rank == 0 else None
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        for i in range(args.steps):
+            graphs[i % layers].replay()
+        end.record(stream)
+        barrier()
+        elapsed_ms = begin.elapsed_time(end)
+        clocks = sampler.stop() if sampler else None
+
+        # ---- end to end: host buffers, copies inside the timed region ---
+        host_in = [tuple(t.cpu().pin_memory() for t in b) for b in batches]
+        host_out = [torch.empty_like(o, device="cpu").pin_memory() for o in outs]
+
+        def e2e_step(index: int) -> None:
+            for source, target in zip(host_in[index], batches[index]):
+                target.copy_(source, non_blocking=True)
+            graphs[index].replay()
+            host_out[index].copy_(outs[index], non_blocking=True)
+            stream.synchronize()
+
+        for i in range(args.warmup):
+            e2e_step(i % layers)
+        barrier()
+        start = time.perf_counter()
+        begin.record(stream)
+        for i in range(args.steps):
+            e2e_step(i % layers)
+        end.record(stream)
+        barrier()
+        e2e_ms = max(begin.elapsed_time(end), 1e3 * (time.perf_counter() - start))
+
+        # ---- per-stage device times (CUDA events on the launching stream) --
+        library = _native.load()
+        stage_ms = {name: 0.0 for name in STAGES}
+        events = [torch.cuda.Event(enable_timing=True) for _ in range(len(STAGES) + 1)]
+        rounds = max(1, min(args.steps, 4 * layers))
+        for i in range(rounds):
+            reader = readers[i % layers]
+            hidden, ids, weights = batches[i % layers]
+            call = reader._call_struct(tokens, hidden, ids, weights, None, outs[i % layers], False)
+            events[0].record(stream)
+            for j, name in enumerate(STAGES):
+                _native.check(getattr(library, name)(
+                    ctypes.byref(reader._layer), workspace.buffer.data_ptr(), workspace.capacity,
+                    ctypes.byref(call), ctypes.c_void_p(stream.cuda_stream)), name)
+                events[j + 1].record(stream)
+            stream.synchronize()
+            for j, name in enumerate(STAGES):
+                stage_ms[name] += events[j].elapsed_time(events[j + 1]) / rounds
+            if i == 0:
+                bytes_by_kernel = algorithmic_bytes(reader, tokens)
+        report = readers[0].report()
+
+    times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+    if distributed:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms = times.tolist()
+    if rank == 0:
+        peak, peak_kind = measured_peaks()
+        total_tokens = tokens * args.steps * world
+        dominant = max(stage_ms, key=stage_ms.get)
+        kernel = KERNEL_OF_STAGE[dominant]
+        kernel_bytes = bytes_by_kernel.get(kernel, 0.0)
+        achieved = kernel_bytes / (stage_ms[dominant] * 1e-3) / 1e9
+        step_ms = elapsed_ms / args.steps
+        layer_gbs = bytes_by_kernel["total"] / (step_ms * 1e-3) / 1e9
+        h2d = sum(t.numel() * t.element_size() for t in host_in[0])
+        d2h = host_out[0].numel() * host_out[0].element_size()
+        line = {
+            "metric": METRIC, "value": total_tokens / (elapsed_ms * 1e-3), "unit": UNIT,
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(shape, plan, tokens, layers, world),
+            "clocks": clocks,
+            "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": len(STAGES) * args.steps,
+            "roofline": {
+                "bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "algorithmic_bytes_per_launch": kernel_bytes,
+                "ms_per_launch": stage_ms[dominant], "peak_source": peak_kind,
+            },
+            "layer_roofline": {
+                "algorithmic_bytes_per_step": bytes_by_kernel["total"], "achieved": layer_gbs,
+                "peak": peak, "unit": "GB/s", "frac": layer_gbs / peak,
+                "frac_of_nominal_8000": layer_gbs / 8000.0,
+            },
+            "stage_ms": {KERNEL_OF_STAGE[k]: round(v, 5) for k, v in stage_ms.items()},
+            "read_cost_bytes_per_token": report["charged_bytes"]
+            / max(1.0, report["reference_bytes"] / plan.native_read_bytes()),
+            "read_fraction": report["read_fraction"],
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_oracle_rate(shape, plan, min(tokens, 64))
+        print(json.dumps(line))
+    if distributed:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__)
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=240)
+    parser.add_argument("--warmup", type=int, default=24)
+    parser.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    parser.add_argument("--tokens", type=int, default=64)
+    parser.add_argument("--layers", type=int, default=12)
+    parser.add_argument("--config", default="qwen3-30b-a3b", choices=sorted(synthetic.CONFIGS))
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    args = parser.parse_args()
+    shape = synthetic.CONFIGS[args.config]
+    plan = compile_budget(
+        hidden_size=shape.hidden, expert_width=shape.width, top_k=shape.top_k,
+        retention=shape.retention, screen_keep=shape.screen_keep,
+    )
+    if args.impl == "reference":
+        if args.steps == 240 and args.warmup == 24:
+            args.steps, args.warmup = 5, 3
+        run_reference(args, shape, plan)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    run_ours(args, shape, plan)
+
+
+if __name__ == "__main__":
+    main()

@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(32) k_route(Layer L, Workspace ws, const void*
 // of each block.  Integer partial dots are summed across coordinate groups in
 // shared memory; each thread then finishes 16/CG rows.
 template <int CG>
-__global__ void k_screen(Layer L, Workspace ws, const uint8_t* padding, int S) {
+__global__ void __launch_bounds__(512) k_screen(Layer L, Workspace ws, const uint8_t* padding, int S) {
   constexpr int RPT = kWordRows / CG;  // rows a thread finishes per block
   constexpr int U = 8;                 // words in flight per thread
   extern __shared__ int smem[];
@@ -994,10 +994,10 @@ static int run_screen(const Bound& b) {
     while (S < b.L.B && pairs * S < 2 * 148) S *= 2;
     if (S > b.L.B) S = b.L.B;
   }
-  // Coordinate groups: as many as keep the CTA within 1024 threads, at most 4.
+  // Coordinate groups: as many as keep the CTA within 512 threads, at most 4.
   int cg = 4;
-  while (cg > 1 && b.L.W * cg > 1024) cg >>= 1;
-  if (b.L.W > 1024) return CFM_E_SHAPE;
+  while (cg > 1 && b.L.W * cg > 512) cg >>= 1;
+  if (b.L.W > 512) return CFM_E_SHAPE;  // I > 4096
   switch (cg) {
     case 4: return launch_screen<4>(b, S);
     case 2: return launch_screen<2>(b, S);
@@ -1007,7 +1007,7 @@ static int run_screen(const Bound& b) {
 
 static int run_select(const Bound& b) {
   const size_t smem = sizeof(uint32_t) * b.L.N;
-  if (smem > 48 * 1024) {
+  if (smem + 2048 > 48 * 1024) {  // static shared memory counts against the default limit
     const cudaError_t err = cudaFuncSetAttribute(
         k_select, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);

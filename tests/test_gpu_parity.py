@@ -1,0 +1,277 @@
+"""GPU parity: the CUDA reader, called through its C ABI, against the CPU oracle and
+the reference's golden vectors on the same seeded inputs.
+
+The oracle is given the reader's own down-column norms (a construction-time
+quantity whose FP32 reduction order differs between devices), as the reference's
+tests do (tests/test_progressive_reader.py:171).
+
+Bars: kept channel indices, kept rotated coordinates, sketch projections and
+scores bit-exact against the oracle (integer dot products and pinned FP32
+arithmetic); selections bit-exact against the reference goldens wherever the
+reference's own two rotations agree; outputs within the reference's tolerance
+(rtol 0.025, atol 0.02) and within 1e-2 relative L2 of the FP32 evaluation.
+"""
+
+import pytest
+import torch
+
+import cases
+from cfm_b200.reader.progressive import ProgressiveReader
+from helpers import bf16_from_bits, golden, prepared, relative_l2, run_oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def make_reader(item, capacity=None, **kwargs):
+    case = item["case"]
+    device = torch.device("cuda:0")
+    sketch = (item["codes"].to(device), _move_statistics(item["statistics"], device))
+    return ProgressiveReader(
+        case.gate_up.to(device),
+        _channel_major(item["down"], device),
+        case.encoder.to(device) if case.encoder is not None else None,
+        case.decoder.to(device) if case.decoder is not None else None,
+        case.plan,
+        capacity or case.hidden.shape[0],
+        sketch=sketch,
+        activation=case.activation,
+        selection_score="point",
+        **kwargs,
+    )
+
+
+def _channel_major(down, device):
+    return down.transpose(1, 2).contiguous().to(device).transpose(1, 2)
+
+
+def _move_statistics(statistics, device):
+    return statistics.permute(0, 2, 3, 1).contiguous().to(device).permute(0, 3, 1, 2)
+
+
+def run_reader(reader, case, **kwargs):
+    device = reader.native_gu.device
+    padding = case.padding.to(device) if case.padding is not None else None
+    out = reader(
+        case.hidden.to(device), case.ids.to(device), case.weights.to(device), padding, **kwargs
+    )
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("name", cases.NAMES)
+def test_reader_matches_oracle_and_golden(oracle, name):
+    item = prepared(name)
+    case, expected = item["case"], golden(name)
+    plan = case.plan
+    tokens, n, f = case.hidden.shape[0], plan.candidate_count, plan.final_count
+    reader = make_reader(item)
+    out = run_reader(reader, case).cpu()
+    want = run_oracle(oracle, item, norms=reader.norms.cpu())
+    active = torch.ones(tokens, dtype=torch.bool)
+    if case.padding is not None:
+        active = ~case.padding
+    # Route.
+    assert torch.equal(reader.ids[:tokens].cpu()[active], want["sorted_ids"][active])
+    assert torch.equal(reader.weights[:tokens].cpu()[active], want["sorted_weights"][active])
+    if plan.completion_count < n:
+        # Kept coordinates and rotated values, bit-exact.
+        assert torch.equal(
+            reader.sketch_coordinates[:tokens].cpu()[active], want["coordinates"][active]
+        )
+        assert torch.equal(reader.sketch_planes[:tokens].cpu()[active], want["planes"][active])
+        # Projections and scores, bit-exact.
+        assert torch.equal(reader.partial[:tokens].cpu()[active], want["partial"][active])
+        assert torch.equal(reader.scores[0][:tokens].cpu()[active], want["scores"][active])
+    # Selection, bit-exact against the oracle ...
+    assert torch.equal(reader.selected[:tokens].cpu()[active], want["selected"][active])
+    assert torch.equal(
+        reader.candidate_ids[-1][:tokens].cpu()[active], want["candidate_ids"][active]
+    )
+    # ... and against the reference golden where its two rotations agree.
+    comparable = active & torch.from_numpy(expected["rotation_agrees"])
+    assert torch.equal(
+        reader.candidate_ids[-1][:tokens].cpu()[comparable],
+        torch.from_numpy(expected["selected_ids"])[comparable],
+    )
+    counts = want["selected"].reshape(tokens, plan.top_k, -1).sum(-1).int()
+    assert torch.equal(reader.counts[:tokens].cpu()[active], counts[active])
+    starts = counts.cumsum(-1) - counts
+    assert torch.equal(reader.starts[:tokens].cpu()[active], starts[active].int())
+    # Output.
+    torch.testing.assert_close(out.float()[active], want["output"][active], rtol=0.025, atol=0.02)
+    reference_out = bf16_from_bits(expected["output_bits"]).float()
+    torch.testing.assert_close(
+        out.float()[comparable], reference_out[comparable], rtol=0.025, atol=0.02
+    )
+    exact = run_oracle(oracle, item, fp32=True, norms=reader.norms.cpu())
+    assert relative_l2(out[active], exact["output"][active]) < 1e-2
+    if case.padding is not None:
+        assert not out[case.padding].any()
+    if reader.rank:
+        torch.testing.assert_close(
+            reader.latent[:tokens].cpu()[active], want["latent"][active], rtol=0.015, atol=0.01
+        )
+
+
+def test_results_do_not_depend_on_batch_or_capacity(oracle):
+    """Each token's selection and output are the same alone, in a batch, or in a larger workspace."""
+    item = prepared("qwen3-e16-t8")
+    case = item["case"]
+    device = torch.device("cuda:0")
+    batch = make_reader(item, capacity=32)
+    full = run_reader(batch, case).clone()
+    kept = batch.candidate_ids[-1][:8].clone()
+    scores = batch.scores[0][:8].clone()
+    single = make_reader(item, capacity=1)
+    for token in range(8):
+        out = single(
+            case.hidden[token : token + 1].to(device),
+            case.ids[token : token + 1].to(device),
+            case.weights[token : token + 1].to(device),
+        )
+        torch.cuda.synchronize()
+        assert torch.equal(single.candidate_ids[-1][0], kept[token])
+        assert torch.equal(single.scores[0][0], scores[token])
+        assert torch.equal(out[0], full[token])
+
+
+def test_repeated_calls_are_bit_identical():
+    item = prepared("qwen35-e16-t4")
+    reader = make_reader(item)
+    first = run_reader(reader, item["case"]).clone()
+    work = reader.read_work.clone()
+    for _ in range(3):
+        reader.workspace.scores.fill_(float("nan"))
+        reader.workspace.partial.fill_(float("nan"))
+        again = run_reader(reader, item["case"])
+        assert torch.equal(first, again)
+    assert torch.equal(reader.read_work, 4 * work)
+
+
+def test_zero_input_keeps_the_first_candidates():
+    item = prepared("zero-input-ties")
+    reader = make_reader(item)
+    out = run_reader(reader, item["case"])
+    f = item["case"].plan.final_count
+    expected = torch.arange(f, dtype=torch.int32, device="cuda").expand(2, -1)
+    assert torch.equal(reader.candidate_ids[-1][:2], expected)
+    assert not out.any()
+
+
+def test_equal_experts_tie_in_slot_order():
+    item = prepared("equal-experts")
+    reader = make_reader(item)
+    run_reader(reader, item["case"])
+    case = item["case"]
+    k, i = case.plan.top_k, case.plan.expert_width
+    scores = reader.scores[0][:3].reshape(3, k, i)
+    assert torch.equal(scores, scores[:, :1].expand(3, k, i))
+    top = (
+        reader.scores[0][:3].cpu().argsort(dim=1, descending=True, stable=True)
+        [:, : case.plan.final_count].sort(dim=1).values
+    )
+    assert torch.equal(reader.candidate_ids[-1][:3].cpu(), top.int())
+
+
+def test_int64_ids_bf16_weights_and_prepared_input(oracle):
+    item = prepared("gemma-gelu")
+    case = item["case"]
+    device = torch.device("cuda:0")
+    reader = make_reader(item)
+    base = run_reader(reader, case).clone()
+    kept = reader.candidate_ids[-1][:4].clone()
+    hidden = case.hidden.to(device)
+    assert reader.prepare_input(hidden)
+    out = reader(hidden, case.ids.to(device).long(), case.weights.to(device), input_prepared=True)
+    torch.cuda.synchronize()
+    assert torch.equal(out, base)
+    assert torch.equal(reader.candidate_ids[-1][:4], kept)
+    # BF16 router weights change the weights, not the contract.
+    out16 = reader(hidden, case.ids.to(device), case.weights.to(device).bfloat16())
+    torch.cuda.synchronize()
+    assert torch.equal(reader.weights[:4], case_sorted_weights(case).to(device))
+    assert torch.isfinite(out16.float()).all()
+
+
+def case_sorted_weights(case):
+    order = case.ids.long().argsort(dim=1, stable=True)
+    return case.weights.bfloat16().float().gather(1, order)
+
+
+def test_read_counters_follow_the_plan():
+    item = prepared("qwen3-e16-t8")
+    case, plan = item["case"], item["case"].plan
+    reader = make_reader(item)
+    run_reader(reader, case)
+    report = reader.report()
+    tokens, rank = 8, reader.rank
+    assert report["reference_bytes"] == tokens * plan.native_read_bytes()
+    assert report["native_expert_coefficient_bytes"] == tokens * plan.selected_weight_bytes()
+    assert report["physical_sketch_bytes"] == tokens * plan.sketch_read_bytes(residual=False)
+    assert report["sketch_bytes"] == tokens * plan.sketch_read_bytes(False, sectors=False)
+    assert report["recovery_bytes"] == tokens * plan.recovery_read_bytes(rank)
+    assert report["selection_parameter_bytes"] == tokens * plan.selection_read_bytes(False)
+    assert report["rotation_sign_bytes"] == tokens * plan.hidden_size
+    charged = tokens * (
+        plan.selected_weight_bytes() + plan.sketch_read_bytes(residual=False)
+        + plan.recovery_read_bytes(rank) + plan.selection_read_bytes(False) + plan.hidden_size
+    )
+    assert report["charged_bytes"] == charged
+    assert report["issued_gate_up_bytes"] == tokens * 4 * plan.hidden_size * plan.final_count
+    assert report["issued_down_bytes"] == tokens * 2 * plan.hidden_size * plan.final_count
+    assert report["issued_recovery_encoder_bytes"] == tokens * 2 * rank * (
+        plan.candidate_count - plan.final_count
+    )
+    assert abs(report["read_fraction"] - 0.1846) < 1e-3
+
+
+def test_contract_violations_raise_before_launch():
+    item = prepared("tiny")
+    case = item["case"]
+    reader = make_reader(item)
+    device = torch.device("cuda:0")
+    hidden, ids, weights = case.hidden.to(device), case.ids.to(device), case.weights.to(device)
+    with pytest.raises(ValueError):
+        reader(hidden.float(), ids, weights)
+    with pytest.raises(ValueError):
+        reader(torch.cat((hidden, hidden)), torch.cat((ids, ids)), torch.cat((weights, weights)))
+    with pytest.raises(ValueError):
+        reader(hidden, ids[:, :1].contiguous(), weights[:, :1].contiguous())
+    with pytest.raises(ValueError):
+        reader(hidden, ids, weights, torch.zeros(4, dtype=torch.uint8, device=device))
+    with pytest.raises(ValueError):
+        ProgressiveReader(
+            case.gate_up.to(device), case.down.to(device), None, None, case.plan, 4,
+            selection_score="point",
+        )  # down is not channel-major
+
+
+def test_cuda_graph_replay_with_new_inputs(oracle):
+    item = prepared("graph-routes")
+    case = item["case"]
+    device = torch.device("cuda:0")
+    reader = make_reader(item)
+    hidden, ids = case.hidden.to(device), case.ids.to(device)
+    weights, padding = case.weights.to(device), case.padding.to(device)
+    out = torch.empty_like(hidden)
+    reader(hidden, ids, weights, padding, out)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        reader(hidden, ids, weights, padding, out)
+    for seed, routes, pad in ((11, [[2, 0], [1, 3]], [False, True]), (29, [[3, 1], [2, 0]], [False, False])):
+        fresh = torch.randn(2, 128, generator=torch.Generator().manual_seed(seed)).bfloat16()
+        hidden.copy_(fresh)
+        ids.copy_(torch.tensor(routes, dtype=torch.int32))
+        padding.copy_(torch.tensor(pad))
+        graph.replay()
+        torch.cuda.synchronize()
+        want = oracle.forward(
+            plan=case.plan, gate_up=case.gate_up, down=item["down"], codes=item["codes"],
+            statistics=item["statistics"], signs=item["signs"], hidden=fresh,
+            ids=torch.tensor(routes), weights=case.weights, encoder=case.encoder,
+            decoder=case.decoder, padding=torch.tensor(pad), norms=reader.norms.cpu(),
+        )
+        active = ~torch.tensor(pad)
+        assert torch.equal(reader.selected[:2].cpu()[active], want["selected"][active])
+        torch.testing.assert_close(out.cpu().float(), want["output"], rtol=0.025, atol=0.02)
