@@ -270,7 +270,7 @@ def workload_config(shape, plan, tokens, layers, gpus) -> dict:
         "top_k": shape.top_k, "recovery_rank": shape.rank, "kept_channels": plan.final_count,
         "screen_coordinates": plan.screen_coordinates, "selection_score": "point",
         "tokens_per_step": tokens, "layers_cycled": layers,
-        "l2": f"steps cycle over {layers} layers with distinct weights and inputs",
+        "l2": f"steps cycle over {layers} layers with distinct weights, inputs and workspaces",
         "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas",
     }
 
@@ -279,7 +279,7 @@ def run_ours(args, shape, plan) -> None:
     import ctypes
 
     from cfm_b200 import _native
-    from cfm_b200.reader.progressive import ProgressiveReader, ReaderWorkspace
+    from cfm_b200.reader.progressive import ProgressiveReader
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -292,12 +292,11 @@ def run_ours(args, shape, plan) -> None:
 
         dist.init_process_group("nccl", device_id=device)
     tokens, layers = args.tokens, args.layers
-    workspace = ReaderWorkspace(plan, shape.experts, shape.rank, tokens, device)
     readers, batches = [], []
     for index in range(layers):
         gate_up, down, router, decoder, encoder, g = device_layer(shape, 1000 * rank + index, device)
         readers.append(ProgressiveReader(
-            gate_up, down, encoder, decoder, plan, tokens, workspace=workspace,
+            gate_up, down, encoder, decoder, plan, tokens,
             selection_score="point", retain_reference_sketch=False,
         ))
         batches.append(device_batch(shape, router, tokens, g, device))
@@ -362,25 +361,40 @@ def run_ours(args, shape, plan) -> None:
         e2e_ms = max(begin.elapsed_time(end), 1e3 * (time.perf_counter() - start))
 
         # ---- per-stage device times (CUDA events on the launching stream) --
+        # Every layer's workspace holds the state of its own last call, so one
+        # stage can be replayed for all L layers back to back: one graph per stage
+        # with L launches, timed as a whole, gives that kernel's mean duration on
+        # data that rotates through the layers like the steps above.
         library = _native.load()
-        stage_ms = {name: 0.0 for name in STAGES}
-        events = [torch.cuda.Event(enable_timing=True) for _ in range(len(STAGES) + 1)]
-        rounds = max(1, min(args.steps, 4 * layers))
-        for i in range(rounds):
-            reader = readers[i % layers]
-            hidden, ids, weights = batches[i % layers]
-            call = reader._call_struct(tokens, hidden, ids, weights, None, outs[i % layers], False)
-            events[0].record(stream)
-            for j, name in enumerate(STAGES):
+        stage_ms = {}
+        calls = [
+            readers[i]._call_struct(tokens, *batches[i], None, outs[i], False)
+            for i in range(layers)
+        ]
+
+        def launch_stage(name: str) -> None:
+            for i in range(layers):
+                reader = readers[i]
                 _native.check(getattr(library, name)(
-                    ctypes.byref(reader._layer), workspace.buffer.data_ptr(), workspace.capacity,
-                    ctypes.byref(call), ctypes.c_void_p(stream.cuda_stream)), name)
-                events[j + 1].record(stream)
+                    ctypes.byref(reader._layer), reader.workspace.buffer.data_ptr(),
+                    reader.workspace.capacity, ctypes.byref(calls[i]),
+                    ctypes.c_void_p(stream.cuda_stream)), name)
+
+        repeats = max(3, min(20, args.steps // layers))
+        for name in STAGES:
+            launch_stage(name)
             stream.synchronize()
-            for j, name in enumerate(STAGES):
-                stage_ms[name] += events[j].elapsed_time(events[j + 1]) / rounds
-            if i == 0:
-                bytes_by_kernel = algorithmic_bytes(reader, tokens)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                launch_stage(name)
+            graph.replay()
+            begin.record(stream)
+            for _ in range(repeats):
+                graph.replay()
+            end.record(stream)
+            stream.synchronize()
+            stage_ms[name] = begin.elapsed_time(end) / (repeats * layers)
+        bytes_by_kernel = algorithmic_bytes(readers[0], tokens)
         report = readers[0].report()
 
     times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)

@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -27,7 +27,7 @@ NVCC_FLAGS = [
 
 # Entry points include/cfm_b200.h declares; `load()` checks each one resolves.
 STAGES = (
-    "cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_select", "cfm_exact",
+    "cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_score", "cfm_select", "cfm_exact",
     "cfm_down", "cfm_encode", "cfm_output", "cfm_reader_forward",
 )
 SYMBOLS = ("cfm_abi_version", "cfm_error_string", "cfm_workspace_layout_for") + STAGES
@@ -52,6 +52,7 @@ class Layer(ctypes.Structure):
         ("gate_up", ctypes.c_void_p),
         ("down", ctypes.c_void_p),
         ("sketch", ctypes.c_void_p),
+        ("sketch_grouped", ctypes.c_void_p),
         ("statistics", ctypes.c_void_p),
         ("norms", ctypes.c_void_p),
         ("geometry", ctypes.c_void_p),
@@ -71,6 +72,8 @@ class Call(ctypes.Structure):
         ("ids_are_int64", ctypes.c_int32),
         ("weights_are_bf16", ctypes.c_int32),
         ("input_prepared", ctypes.c_int32),
+        ("scores_ready", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
         ("hidden", ctypes.c_void_p),
         ("ids", ctypes.c_void_p),
         ("weights", ctypes.c_void_p),
@@ -83,7 +86,7 @@ _LAYOUT_ARRAYS = (
     "ids", "weights", "norms", "planes", "coordinates", "quantized", "exponents", "parts",
     "counters", "partial", "scores", "selected", "completed", "candidate_ids", "counts",
     "starts", "tile_starts", "activations", "exact", "down_parts", "encoder_parts", "latent",
-    "status",
+    "status", "limbs", "group_offsets", "group_pairs",
 )
 
 

@@ -50,6 +50,9 @@ struct Workspace {
   float* encoder_parts;
   float* latent;
   int32_t* status;
+  int8_t* limbs;
+  int32_t* group_offsets;
+  int32_t* group_pairs;
   int32_t parts_tokens;
   int32_t down_tiles;
   int32_t encoder_tiles;
@@ -62,6 +65,7 @@ struct Layer {  // device-visible copy of cfm_layer with typed pointers
   const __nv_bfloat16* gate_up;
   const __nv_bfloat16* down;
   const uint32_t* sketch;
+  const uint32_t* sketch_grouped;
   const __half* statistics;
   const float* norms;
   const float* geometry;
@@ -117,6 +121,9 @@ static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layou
   o->encoder_parts = take(4 * C * K * o->encoder_tiles * (R ? R : 1));
   o->latent = take(4 * C * (R ? R : 1));
   o->status = take(16);
+  o->limbs = take(C * B * 3 * kBlock);
+  o->group_offsets = take(4 * (static_cast<int64_t>(l->experts > 0 ? l->experts : 1) + 1));
+  o->group_pairs = take(4 * C * K);
   o->bytes = at;
   return 0;
 }
@@ -147,6 +154,9 @@ static Workspace bind(const cfm_workspace_layout& o, void* base, int32_t capacit
   w.encoder_parts = reinterpret_cast<float*>(p + o.encoder_parts);
   w.latent = reinterpret_cast<float*>(p + o.latent);
   w.status = reinterpret_cast<int32_t*>(p + o.status);
+  w.limbs = reinterpret_cast<int8_t*>(p + o.limbs);
+  w.group_offsets = reinterpret_cast<int32_t*>(p + o.group_offsets);
+  w.group_pairs = reinterpret_cast<int32_t*>(p + o.group_pairs);
   w.parts_tokens = o.parts_tokens;
   w.down_tiles = o.down_tiles;
   w.encoder_tiles = o.encoder_tiles;
@@ -173,6 +183,7 @@ static Layer device_layer(const cfm_layer* l) {
   d.gate_up = static_cast<const __nv_bfloat16*>(l->gate_up);
   d.down = static_cast<const __nv_bfloat16*>(l->down);
   d.sketch = l->sketch;
+  d.sketch_grouped = l->sketch_grouped;
   d.statistics = static_cast<const __half*>(l->statistics);
   d.norms = l->norms;
   d.geometry = l->geometry;
@@ -261,6 +272,18 @@ __global__ void __launch_bounds__(kBlock) k_prepare(Layer L, Workspace ws,
     ws.coordinates[out] = c;
     ws.quantized[out] = q;
   }
+  {
+    // Balanced base-256 digits of q (zero for dropped coordinates), in natural
+    // coordinate order: q = l0 + 256 l1 + 65536 l2, each digit an int8.
+    const int l0 = static_cast<int8_t>(q & 0xff);
+    const int q1 = (q - l0) >> 8;
+    const int l1 = static_cast<int8_t>(q1 & 0xff);
+    const int l2 = (q1 - l1) >> 8;
+    int8_t* limb = ws.limbs + (static_cast<size_t>(t) * L.B + b) * 3 * kBlock + c;
+    limb[0] = static_cast<int8_t>(l0);
+    limb[kBlock] = static_cast<int8_t>(l1);
+    limb[2 * kBlock] = static_cast<int8_t>(l2);
+  }
   int qsum = q;
 #pragma unroll
   for (int w = 16; w; w >>= 1) {
@@ -331,18 +354,15 @@ __global__ void __launch_bounds__(512) k_screen(Layer L, Workspace ws, const uin
   int* sq = smem;              // [128] fixed-point values of the block
   int* sc = sq + kBlock;       // [128] their coordinates
   int* red = sc + kBlock;      // [CG * 16 * W] partial dots (CG > 1)
-  float* proj = reinterpret_cast<float*>(red + (CG > 1 ? CG * kWordRows * W : 0));  // [2I]
   __shared__ int s_last;
 
   const int pair = blockIdx.x, split = blockIdx.y;
   const int t = pair / L.K, slot = pair - t * L.K;
   const int tid = threadIdx.x, wi = tid % W, cg = tid / W;
   const int e = ws.ids[pair];
-  const size_t cand0 = static_cast<size_t>(t) * L.N + static_cast<size_t>(slot) * L.I;
   if ((padding && padding[t]) || e < 0) {
     if (split == 0) {
       for (int c = tid; c < L.I; c += threads) {
-        ws.scores[cand0 + c] = 0.0f;
         ws.partial[static_cast<size_t>(t) * 2 * L.N + slot * L.I + c] = 0.0f;
         ws.partial[static_cast<size_t>(t) * 2 * L.N + L.N + slot * L.I + c] = 0.0f;
       }
@@ -430,37 +450,293 @@ __global__ void __launch_bounds__(512) k_screen(Layer L, Workspace ws, const uin
     }
   }
 
+  float* gate_out = ws.partial + static_cast<size_t>(t) * 2 * L.N + static_cast<size_t>(slot) * L.I;
+  float* up_out = gate_out + L.N;
   if (S == 1) {
 #pragma unroll
-    for (int r = 0; r < RPT; ++r) proj[row0 + r] = run[r];
-  } else {
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned old = atomicAdd(&ws.counters[pair], 1u);
-      s_last = (old == static_cast<unsigned>(S - 1));
-      if (s_last) ws.counters[pair] = 0;
+    for (int r = 0; r < RPT; ++r) {
+      const int row = row0 + r;
+      (row < L.I ? gate_out[row] : up_out[row - L.I]) = run[r];
     }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    // Sum the per-block products in block order.
-    for (int row = tid; row < rows; row += threads) {
-      float s = 0.0f;
-      const float* p = ws.parts + static_cast<size_t>(pair) * L.B * rows + row;
-      for (int b = 0; b < L.B; ++b) s = __fadd_rn(s, __ldcg(p + static_cast<size_t>(b) * rows));
-      proj[row] = s;
-    }
+    return;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned old = atomicAdd(&ws.counters[pair], 1u);
+    s_last = (old == static_cast<unsigned>(S - 1));
+    if (s_last) ws.counters[pair] = 0;
   }
   __syncthreads();
-  const float weight = ws.weights[pair];
-  for (int c = tid; c < L.I; c += threads) {
-    const float g = proj[c], u = proj[L.I + c];
-    ws.partial[static_cast<size_t>(t) * 2 * L.N + slot * L.I + c] = g;
-    ws.partial[static_cast<size_t>(t) * 2 * L.N + L.N + slot * L.I + c] = u;
-    const float norm = L.norms[static_cast<size_t>(e) * L.I + c];
-    ws.scores[cand0 + c] = point_score(g, u, norm, weight, L.activation);
+  if (!s_last) return;
+  __threadfence();
+  // The last split to arrive sums the per-block products in block order.
+  for (int row = tid; row < rows; row += threads) {
+    float s = 0.0f;
+    const float* p = ws.parts + static_cast<size_t>(pair) * L.B * rows + row;
+    for (int b = 0; b < L.B; ++b) s = __fadd_rn(s, __ldcg(p + static_cast<size_t>(b) * rows));
+    (row < L.I ? gate_out[row] : up_out[row - L.I]) = s;
   }
+}
+
+// ---------------------------------------------------------------------------
+// grouped screen: pairs grouped by expert, int8 tensor-core dot products
+// ---------------------------------------------------------------------------
+// Lists the active (token, slot) pairs of every local expert.  One CTA; dynamic
+// shared memory: 2 * E counters.  The order of an expert's pairs is whatever the
+// atomics produce; every pair's result is independent of it.
+__global__ void __launch_bounds__(1024) k_group(Layer L, Workspace ws, const uint8_t* padding,
+                                                int T) {
+  extern __shared__ int group_smem[];
+  int* count = group_smem;
+  int* cursor = group_smem + L.E;
+  const int tid = threadIdx.x, pairs = T * L.K;
+  for (int e = tid; e < L.E; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) {
+    const int e = ws.ids[p];
+    if (e >= 0 && !(padding && padding[p / L.K])) atomicAdd(&count[e], 1);
+  }
+  __syncthreads();
+  if (tid < 32) {  // exclusive scan over experts, one warp
+    int carry = 0;
+    for (int base = 0; base < L.E; base += 32) {
+      const int e = base + tid;
+      const int mine = e < L.E ? count[e] : 0;
+      int scan = mine;
+#pragma unroll
+      for (int w = 1; w < 32; w <<= 1) {
+        const int o = __shfl_up_sync(kFull, scan, w);
+        if (tid >= w) scan += o;
+      }
+      if (e < L.E) {
+        cursor[e] = carry + scan - mine;
+        ws.group_offsets[e] = carry + scan - mine;
+      }
+      carry += __shfl_sync(kFull, scan, 31);
+    }
+    if (tid == 0) ws.group_offsets[L.E] = carry;
+  }
+  __syncthreads();
+  for (int p = tid; p < pairs; p += blockDim.x) {
+    const int e = ws.ids[p];
+    if (e >= 0 && !(padding && padding[p / L.K])) ws.group_pairs[atomicAdd(&cursor[e], 1)] = p;
+  }
+}
+
+// Sixteen 2-bit codes of one 32-bit word -> four int8x4 registers of trits.
+// The grouped layout stores coordinate c of a word at bit 4c (c < 4),
+// 4(c-4)+2 (c < 8), 16+4(c-8) (c < 12), 18+4(c-12) otherwise, so that four
+// masked shifts yield byte-permute selectors; the permute picks -1, 0, +1 from
+// a register table.
+__device__ __forceinline__ void decode_word(uint32_t w, uint32_t& c0, uint32_t& c1, uint32_t& c2,
+                                            uint32_t& c3) {
+  constexpr uint32_t table = 0x000100ffu;  // byte 0 = -1, byte 1 = 0, byte 2 = +1
+  c0 = __byte_perm(table, 0u, w & 0x3333u);
+  c1 = __byte_perm(table, 0u, (w >> 2) & 0x3333u);
+  c2 = __byte_perm(table, 0u, (w >> 16) & 0x3333u);
+  c3 = __byte_perm(table, 0u, (w >> 18) & 0x3333u);
+}
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                       uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+constexpr int kGroupWarps = 8;                   // 16 sketch rows per warp
+constexpr int kGroupRows = kGroupWarps * 16;     // rows per CTA
+constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kLimbBlock = 3 * kBlock + 8;       // bytes of one (token, block) in shared memory
+constexpr int kPrefetch = 4;                     // rotation blocks of sketch words in flight
+
+// Bytes between token slots in shared memory: B blocks, padded so that the
+// stride in 32-bit words is 2 modulo 32 (conflict-free 8-byte fragment loads).
+__host__ __device__ inline int limb_slot_stride(int B) {
+  const int words = B * kLimbBlock / 4;
+  return (words + ((2 - words % 32) + 32) % 32) * 4;
+}
+
+// grid (ceil(2I / 128), E), 256 threads, dynamic shared memory
+// 8 NT * (limb_slot_stride(B) + 4 B) + 32 NT bytes.  A CTA owns 128 sketch rows
+// of one expert.  It first stages the int8 digits of all rotation blocks of up
+// to 8 NT of the expert's tokens in shared memory; then every warp walks the
+// rotation blocks in order on its own (no CTA barrier): it decodes its 16 rows
+// x 128 coordinates into int8 fragments and multiplies them with the digits
+// (m16n8k32, exact int32 sums), keeping sketch words of the next blocks in
+// flight in registers.  Token slot n * 8 + j of a pass is column j of tile n.
+template <int NT>
+__global__ void __launch_bounds__(kGroupThreads) k_screen_grouped(Layer L, Workspace ws) {
+  constexpr int kSlots = NT * 8;
+  extern __shared__ __align__(16) int8_t group_shared[];
+  const int stride = limb_slot_stride(L.B);
+  int8_t* limb_smem = group_shared;                                             // [kSlots][stride]
+  int* exponent_smem = reinterpret_cast<int*>(group_shared + kSlots * stride);  // [kSlots][B]
+  int* pair_smem = exponent_smem + kSlots * L.B;                                // [kSlots]
+  const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, tq = lane & 3;
+  const int first = ws.group_offsets[e], total = ws.group_offsets[e + 1] - first;
+  if (total == 0) return;
+  const int rows = 2 * L.I;
+  const int r0 = blockIdx.x * kGroupRows + warp * 16;
+  const bool live = r0 < rows;  // whole warps are in or out: 2I is a multiple of 32
+  const int row_a = r0 + g, row_b = r0 + g + 8;
+  constexpr int kPieces = 3 * kBlock / 16;  // 16-byte pieces of one (token, block)
+
+  for (int base = 0; base < total; base += kSlots) {
+    const int count = min(kSlots, total - base);
+    __syncthreads();
+    if (tid < kSlots) pair_smem[tid] = tid < count ? ws.group_pairs[first + base + tid] : -1;
+    __syncthreads();
+    // Stage digits and exponents of every block of this pass's tokens.
+    const int pieces = kSlots * L.B * kPieces;
+    for (int index = tid; index < pieces; index += kGroupThreads) {
+      const int slot = index / (L.B * kPieces);
+      const int rest = index - slot * L.B * kPieces;
+      const int b = rest / kPieces, piece = rest - b * kPieces;
+      const int pair = pair_smem[slot];
+      uint4 digits = make_uint4(0, 0, 0, 0);
+      if (pair >= 0) {
+        const size_t tb = static_cast<size_t>(pair / L.K) * L.B + b;
+        digits = *reinterpret_cast<const uint4*>(ws.limbs + tb * 3 * kBlock + piece * 16);
+      }
+      int8_t* dst = limb_smem + slot * stride + b * kLimbBlock + piece * 16;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(digits.x, digits.y);
+      *reinterpret_cast<uint2*>(dst + 8) = make_uint2(digits.z, digits.w);
+    }
+    for (int index = tid; index < kSlots * L.B; index += kGroupThreads) {
+      const int slot = index / L.B, b = index - slot * L.B;
+      const int pair = pair_smem[slot];
+      exponent_smem[index] =
+          pair >= 0 ? ws.exponents[2 * (static_cast<size_t>(pair / L.K) * L.B + b)] : 0;
+    }
+    __syncthreads();
+    if (!live) continue;
+
+    auto sketch_at = [&](int b, int row) {
+      return reinterpret_cast<const uint2*>(
+                 L.sketch_grouped +
+                 ((static_cast<size_t>(e) * L.B + b) * rows + row) * (kBlock / 16)) + tq;
+    };
+    auto scale_at = [&](int b, int row) {
+      return L.statistics[(static_cast<size_t>(e) * L.B + b) * 2 * rows + row];
+    };
+    uint2 word_a[kPrefetch], word_b[kPrefetch];
+    __half scale_a[kPrefetch], scale_b[kPrefetch];
+#pragma unroll
+    for (int u = 0; u < kPrefetch; ++u) {
+      if (u < L.B) {
+        word_a[u] = *sketch_at(u, row_a);
+        word_b[u] = *sketch_at(u, row_b);
+        scale_a[u] = scale_at(u, row_a);
+        scale_b[u] = scale_at(u, row_b);
+      }
+    }
+    float run[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) run[n][i] = 0.0f;
+
+    for (int b0 = 0; b0 < L.B; b0 += kPrefetch) {
+#pragma unroll
+      for (int u = 0; u < kPrefetch; ++u) {
+        const int b = b0 + u;
+        if (b >= L.B) break;
+        const uint2 cur_a = word_a[u], cur_b = word_b[u];
+        const float cur_scale_a = __half2float(scale_a[u]), cur_scale_b = __half2float(scale_b[u]);
+        if (b + kPrefetch < L.B) {
+          word_a[u] = *sketch_at(b + kPrefetch, row_a);
+          word_b[u] = *sketch_at(b + kPrefetch, row_b);
+          scale_a[u] = scale_at(b + kPrefetch, row_a);
+          scale_b[u] = scale_at(b + kPrefetch, row_b);
+        }
+        int acc[NT][3][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+          for (int j = 0; j < 3; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[n][j][i] = 0;
+        // Thread (g, tq) holds coordinates 32 tq .. 32 tq + 31 of rows g and g+8:
+        // k-step m uses coordinates 32 tq + 8 m .. + 7.
+        uint32_t fa[8], fb[8];
+        decode_word(cur_a.x, fa[0], fa[1], fa[2], fa[3]);
+        decode_word(cur_a.y, fa[4], fa[5], fa[6], fa[7]);
+        decode_word(cur_b.x, fb[0], fb[1], fb[2], fb[3]);
+        decode_word(cur_b.y, fb[4], fb[5], fb[6], fb[7]);
+        const int8_t* limbs = limb_smem + b * kLimbBlock + 32 * tq;
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+#pragma unroll
+          for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int j = 0; j < 3; ++j) {
+              const uint2 bv = *reinterpret_cast<const uint2*>(
+                  limbs + (n * 8 + g) * stride + j * kBlock + 8 * m);
+              mma_s8(acc[n][j], fa[2 * m], fb[2 * m], fa[2 * m + 1], fb[2 * m + 1], bv.x, bv.y);
+            }
+          }
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int dot = acc[n][0][i] + acc[n][1][i] * 256 + acc[n][2][i] * 65536;
+            const int be = exponent_smem[(n * 8 + 2 * tq + (i & 1)) * L.B + b];
+            const float unscale =
+                __uint_as_float(static_cast<uint32_t>(127 + be - kQuantBits) << 23);
+            const float d = __fmul_rn(__int2float_rn(dot), unscale);
+            const float prod = __fmul_rn(i < 2 ? cur_scale_a : cur_scale_b, d);
+            run[n][i] = __fadd_rn(run[n][i], prod);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int pair = pair_smem[n * 8 + 2 * tq + (i & 1)];
+        if (pair < 0) continue;
+        const int row = (i < 2) ? row_a : row_b;
+        const int t = pair / L.K, slot = pair - t * L.K;
+        float* out = ws.partial + static_cast<size_t>(t) * 2 * L.N + static_cast<size_t>(slot) * L.I;
+        (row < L.I ? out[row] : out[L.N + row - L.I]) = run[n][i];
+      }
+    }
+  }
+}
+
+// grid (T, ceil(N / 256)), 256 threads: zero the projections of remote or padded
+// slots (the grouped screen writes only live pairs).
+__global__ void k_clear_dead(Layer L, Workspace ws, const uint8_t* padding) {
+  const int t = blockIdx.x, i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= L.N) return;
+  const int slot = i / L.I;
+  if ((padding && padding[t]) || ws.ids[static_cast<size_t>(t) * L.K + slot] < 0) {
+    ws.partial[static_cast<size_t>(t) * 2 * L.N + i] = 0.0f;
+    ws.partial[static_cast<size_t>(t) * 2 * L.N + L.N + i] = 0.0f;
+  }
+}
+
+// grid (T, ceil(N / 256)), 256 threads: scores from projections (used when the
+// scores are exchanged between ranks before selection).
+__global__ void k_score(Layer L, Workspace ws, const uint8_t* padding) {
+  const int t = blockIdx.x, i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= L.N) return;
+  const int slot = i / L.I, c = i - slot * L.I;
+  const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
+  float value = 0.0f;
+  if (e >= 0 && !(padding && padding[t])) {
+    const float* gate = ws.partial + static_cast<size_t>(t) * 2 * L.N;
+    value = point_score(gate[i], gate[L.N + i], L.norms[static_cast<size_t>(e) * L.I + c],
+                        ws.weights[static_cast<size_t>(t) * L.K + slot], L.activation);
+  }
+  ws.scores[static_cast<size_t>(t) * L.N + i] = value;
 }
 
 // ---------------------------------------------------------------------------
@@ -472,7 +748,8 @@ __device__ __forceinline__ int64_t sector_run(int64_t bytes) { return (bytes + 3
 
 // grid (T), 1024 threads, dynamic shared memory: N keys.
 __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws,
-                                                           const uint8_t* padding) {
+                                                           const uint8_t* padding,
+                                                           int scores_ready) {
   extern __shared__ uint32_t keys[];
   __shared__ int hist[256];
   __shared__ int warp_above[32], warp_ties[32];
@@ -491,8 +768,23 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
   uint32_t cut = 0;
   int take_ties = 0;
   if (screened) {
-    const float* score = ws.scores + static_cast<size_t>(t) * N;
-    for (int i = tid; i < N; i += kSelectThreads) keys[i] = __float_as_uint(score[i]);
+    float* score = ws.scores + static_cast<size_t>(t) * N;
+    if (scores_ready) {
+      for (int i = tid; i < N; i += kSelectThreads) keys[i] = __float_as_uint(score[i]);
+    } else {
+      // Score every candidate from its sketch projections (zero for remote slots).
+      const float* gate = ws.partial + static_cast<size_t>(t) * 2 * N;
+      for (int i = tid; i < N; i += kSelectThreads) {
+        const int slot = i / I, c = i - slot * I;
+        const int e = ws.ids[static_cast<size_t>(t) * K + slot];
+        float value = 0.0f;
+        if (e >= 0)
+          value = point_score(gate[i], gate[N + i], L.norms[static_cast<size_t>(e) * I + c],
+                              ws.weights[static_cast<size_t>(t) * K + slot], L.activation);
+        score[i] = value;
+        keys[i] = __float_as_uint(value);
+      }
+    }
     // Radix search, most significant byte first, for the F-th largest key.
     uint32_t prefix = 0, mask = 0;
     int remaining = F;
@@ -973,8 +1265,7 @@ static int run_route(const Bound& b, const cfm_call* call) {
 template <int CG>
 static int launch_screen(const Bound& b, int S) {
   const int threads = b.L.W * CG;
-  const size_t smem = sizeof(int) * (2 * kBlock + (CG > 1 ? CG * kWordRows * b.L.W : 0)) +
-                      sizeof(float) * 2 * b.L.I;
+  const size_t smem = sizeof(int) * (2 * kBlock + (CG > 1 ? CG * kWordRows * b.L.W : 0));
   if (smem > 48 * 1024) {
     const cudaError_t err = cudaFuncSetAttribute(
         k_screen<CG>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
@@ -984,8 +1275,46 @@ static int launch_screen(const Bound& b, int S) {
   return launched();
 }
 
+static int run_screen_grouped(const Bound& b) {
+  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
+  int rc = launched();
+  if (rc) return rc;
+  const dim3 grid((2 * b.L.I + kGroupRows - 1) / kGroupRows, b.L.E);
+  // Two tiles of eight tokens per pass once experts hold more than six pairs on
+  // average and the digits of sixteen tokens still fit in shared memory.
+  const auto shared = [&](int slots) {
+    return static_cast<size_t>(slots) * (limb_slot_stride(b.L.B) + 4 * b.L.B) + 4 * slots;
+  };
+  const bool wide = static_cast<int64_t>(b.T) * b.L.K > 6LL * b.L.E && shared(16) <= 100 * 1024;
+  const size_t smem = shared(wide ? 16 : 8);
+  if (smem > 200 * 1024) return CFM_E_SHAPE;  // H beyond 128 * 64
+  const void* kernel = wide ? reinterpret_cast<const void*>(k_screen_grouped<2>)
+                            : reinterpret_cast<const void*>(k_screen_grouped<1>);
+  if (smem > 48 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(
+        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  if (wide) {
+    k_screen_grouped<2><<<grid, kGroupThreads, smem, b.stream>>>(b.L, b.ws);
+  } else {
+    k_screen_grouped<1><<<grid, kGroupThreads, smem, b.stream>>>(b.L, b.ws);
+  }
+  if ((rc = launched())) return rc;
+  if (b.padding || b.L.expert_map) {
+    k_clear_dead<<<dim3(b.T, (b.L.N + 255) / 256), 256, 0, b.stream>>>(b.L, b.ws, b.padding);
+    rc = launched();
+  }
+  return rc;
+}
+
+// Batch size from which the screen runs expert-major on the tensor cores.
+constexpr int kGroupedScreenTokens = 8;
+
 static int run_screen(const Bound& b) {
   if (b.L.F >= b.L.N) return 0;
+  if (b.L.sketch_grouped && b.T >= kGroupedScreenTokens && b.L.E <= 4096)
+    return run_screen_grouped(b);
   // Split the rotation blocks across CTAs while the batch is too small to fill
   // the 148 SMs; large batches keep each pair's blocks in one CTA.
   const int pairs = b.T * b.L.K;
@@ -1005,14 +1334,20 @@ static int run_screen(const Bound& b) {
   }
 }
 
-static int run_select(const Bound& b) {
+static int run_select(const Bound& b, int scores_ready) {
   const size_t smem = sizeof(uint32_t) * b.L.N;
   if (smem + 2048 > 48 * 1024) {  // static shared memory counts against the default limit
     const cudaError_t err = cudaFuncSetAttribute(
         k_select, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);
   }
-  k_select<<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding);
+  k_select<<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready);
+  return launched();
+}
+
+static int run_score(const Bound& b) {
+  if (b.L.F >= b.L.N) return 0;
+  k_score<<<dim3(b.T, (b.L.N + 255) / 256), 256, 0, b.stream>>>(b.L, b.ws, b.padding);
   return launched();
 }
 
@@ -1090,7 +1425,8 @@ int cfm_workspace_layout_for(const cfm_layer* layer, int32_t capacity,
 CFM_STAGE(cfm_prepare_input, return run_prepare(b, call);)
 CFM_STAGE(cfm_route, return run_route(b, call);)
 CFM_STAGE(cfm_screen, return run_screen(b);)
-CFM_STAGE(cfm_select, return run_select(b);)
+CFM_STAGE(cfm_select, return run_select(b, call->scores_ready);)
+CFM_STAGE(cfm_score, return run_score(b);)
 CFM_STAGE(cfm_exact, return run_exact(b, call);)
 CFM_STAGE(cfm_down, return run_down(b);)
 CFM_STAGE(cfm_encode, return run_encode(b);)
@@ -1104,7 +1440,7 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
   if (!call->input_prepared && (rc = run_prepare(b, call))) return rc;
   if ((rc = run_route(b, call))) return rc;
   if ((rc = run_screen(b))) return rc;
-  if ((rc = run_select(b))) return rc;
+  if ((rc = run_select(b, 0))) return rc;
   if ((rc = run_exact(b, call))) return rc;
   if ((rc = run_down(b))) return rc;
   if ((rc = run_encode(b))) return rc;

@@ -23,7 +23,7 @@ from torch import Tensor
 from .. import _native
 from ..activation import ACTIVATION_CODES, GatedActivation
 from .budget import BudgetPlan
-from .sketch import block_hadamard_signs, build_sketch, repack_sketch
+from .sketch import block_hadamard_signs, build_sketch, repack_sketch, repack_sketch_grouped
 from .budget import sketch_storage_bytes
 
 SelectionScore = Literal["recovery-aware", "point"]
@@ -33,6 +33,9 @@ SCORE_CODES = {"point": 0, "recovery-aware": 1}
 # path whose results do not depend on them.
 GROUPED_TOKENS = 32
 GROUPED_SCREEN_TOKENS = 64
+# Batch size from which the library screens expert-major; readers with a smaller
+# capacity do not keep the row-major sketch copy that path reads.
+GROUPED_SCREEN_MIN_TOKENS = 8
 
 
 def channel_major_down(weight: Tensor) -> Tensor:
@@ -52,7 +55,8 @@ _TORCH_TYPES = {
     "completed": torch.bool, "candidate_ids": torch.int32, "counts": torch.int32,
     "starts": torch.int32, "tile_starts": torch.int32, "activations": torch.bfloat16,
     "exact": torch.float32, "down_parts": torch.float32, "encoder_parts": torch.float32,
-    "latent": torch.float32, "status": torch.int32,
+    "latent": torch.float32, "status": torch.int32, "limbs": torch.int8,
+    "group_offsets": torch.int32, "group_pairs": torch.int32,
 }
 
 
@@ -113,7 +117,8 @@ class ReaderWorkspace:
             "activations": (c, n), "exact": (c, 2, f),
             "down_parts": (c, layout.down_tiles, h),
             "encoder_parts": (c, k, layout.encoder_tiles, r), "latent": (c, r),
-            "status": (4,),
+            "status": (4,), "limbs": (c, blocks, 3, 128),
+            "group_offsets": (experts + 1,), "group_pairs": (c * k,),
         }
         for name, shape in shapes.items():
             setattr(self, name, self._view(name, shape))
@@ -267,8 +272,16 @@ class ProgressiveReader:
         self.sketch_statistics = statistics
         # Kernel layout: two bits per trit, [E, H, 2I/16] words.
         self.sketch_words = repack_sketch(codes, 2 * i, h)
+        # Row-major copy for the expert-major screen of batches of 8 tokens and more.
+        self.sketch_grouped_words = (
+            repack_sketch_grouped(codes, 2 * i, h) if max_tokens >= GROUPED_SCREEN_MIN_TOKENS else None
+        )
         self.sketch_codes = codes if retain_reference_sketch else None
-        self.sketch_resident_bytes = self.sketch_words.numel() * 4 + statistics.numel() * 2
+        self.sketch_resident_bytes = (
+            self.sketch_words.numel() * 4
+            + statistics.numel() * 2
+            + (self.sketch_grouped_words.numel() * 4 if self.sketch_grouped_words is not None else 0)
+        )
 
         self.norms = down.float().square().sum(1).sqrt().contiguous()
         self.native_gu = gate_up.detach()
@@ -326,6 +339,9 @@ class ProgressiveReader:
         layer.gate_up = self.native_gu.data_ptr()
         layer.down = self.down.data_ptr()
         layer.sketch = self.sketch_words.data_ptr()
+        layer.sketch_grouped = (
+            self.sketch_grouped_words.data_ptr() if self.sketch_grouped_words is not None else None
+        )
         layer.statistics = statistics.data_ptr()
         layer.norms = self.norms.data_ptr()
         layer.geometry = None
@@ -470,7 +486,9 @@ class ProgressiveReader:
             self._stage("cfm_route", call)
             if screened:
                 self._stage("cfm_screen", call)
+                self._stage("cfm_score", call)
                 dist.all_reduce(self.scores[0][:tokens], group=self.ep_group)
+                call.scores_ready = 1
             self._stage("cfm_select", call)
             self._stage("cfm_exact", call)
             self._stage("cfm_down", call)

@@ -222,3 +222,32 @@ def repack_sketch(codes: Tensor, rows: int, hidden: int) -> Tensor:
         word = (grouped << shifts).sum(-1)  # < 2**32, held in int64
         out[expert] = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
     return out
+
+
+# Bit position of coordinate c (0..15) inside a word of the grouped layout: four
+# masked shifts of the word then give the byte-permute selectors of coordinates
+# 0-3, 4-7, 8-11 and 12-15.
+GROUPED_BIT = tuple(
+    4 * c if c < 4 else 4 * (c - 4) + 2 if c < 8 else 16 + 4 * (c - 8) if c < 12 else 18 + 4 * (c - 12)
+    for c in range(16)
+)
+
+
+def repack_sketch_grouped(codes: Tensor, rows: int, hidden: int) -> Tensor:
+    """Re-lay reference codes row-major for the expert-major screen, int32 `[E, B, rows, 8]`.
+
+    Word w of (block b, row r) holds coordinates 16 w .. 16 w + 15 of that block,
+    trit + 1 in two bits at the positions of `GROUPED_BIT`.  A row's 128
+    coordinates of one block are 32 contiguous bytes and consecutive rows follow
+    each other, so a warp reading 16 rows reads 512 contiguous bytes.
+    """
+    experts = codes.shape[0]
+    blocks = hidden // ROTATION_BLOCK
+    out = torch.empty((experts, blocks, rows, 8), device=codes.device, dtype=torch.int32)
+    shifts = torch.tensor(GROUPED_BIT, device=codes.device, dtype=torch.int64)
+    for expert in range(experts):
+        digits = unpack_sketch(codes[expert], rows, hidden).to(torch.int64) + 1  # [rows, H]
+        grouped = digits.reshape(rows, blocks, 8, 16).permute(1, 0, 2, 3)
+        word = (grouped << shifts).sum(-1)
+        out[expert] = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
+    return out

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 1
+#define CFM_ABI_VERSION 2
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -60,7 +60,8 @@ typedef struct cfm_layer {
   int32_t reserved;
   const void* gate_up;       /* bf16 [E, 2I, H] contiguous                      */
   const void* down;          /* bf16 physical [E, I, H] (channel-major)         */
-  const uint32_t* sketch;    /* kernel layout [E, H, 2I/16], 2 bits per trit    */
+  const uint32_t* sketch;    /* coordinate-major layout [E, H, 2I/16], 2 bits per trit */
+  const uint32_t* sketch_grouped; /* row-major layout [E, B, 2I, 8] or NULL     */
   const void* statistics;    /* fp16 physical [E, B, 2, 2I]: scale, variance    */
   const float* norms;        /* f32 [E, I], down-column norms                   */
   const float* geometry;     /* f32 [E, I, 2] or NULL (recovery-aware score)    */
@@ -78,6 +79,8 @@ typedef struct cfm_call {
   int32_t ids_are_int64;  /* ids element type: 0 int32, 1 int64                */
   int32_t weights_are_bf16; /* router weight type: 0 float32, 1 bfloat16       */
   int32_t input_prepared; /* 1: cfm_prepare_input already ran for these rows   */
+  int32_t scores_ready;   /* 1: cfm_select reads `scores` instead of computing */
+  int32_t reserved;
   const void* hidden;     /* bf16 [T, H]                                       */
   const void* ids;        /* [T, K] router expert ids (global ids under EP)    */
   const void* weights;    /* [T, K] router weights                             */
@@ -114,6 +117,9 @@ typedef struct cfm_workspace_layout {
   int64_t encoder_parts;  /* f32 [C, K, encoder_tiles, R]                       */
   int64_t latent;         /* f32 [C, R]                                         */
   int64_t status;         /* i32 [4] device-side error flags (zero = healthy)   */
+  int64_t limbs;          /* i8  [C, B, 3, 128] base-256 digits of `quantized`  */
+  int64_t group_offsets;  /* i32 [E + 1] first pair of every expert             */
+  int64_t group_pairs;    /* i32 [C * K] (token, slot) pairs grouped by expert  */
   int32_t parts_tokens;   /* tokens the split screen can serve                  */
   int32_t down_tiles;     /* ceil(F / 128) + K - 1                              */
   int32_t encoder_tiles;  /* ceil(I / 64)                                       */
@@ -145,12 +151,22 @@ int cfm_prepare_input(const cfm_layer* layer, void* workspace, int32_t capacity,
 int cfm_route(const cfm_layer* layer, void* workspace, int32_t capacity,
               const cfm_call* call, void* stream);
 
-/* Screen: sketch GEMV of every candidate channel of every routed local expert
- * and the selection score.  Writes `partial` and `scores`; rows of remote or
- * padded slots are zero.  Replaces: _sketch_screen and its helpers
- * (progressive.py:478-1066), _screen_score (:1274-1353). */
+/* Screen: sketch projections of every candidate channel of every routed local
+ * expert.  Writes `partial`; rows of remote or padded slots are zero.  Small
+ * batches run one GEMV per (token, expert) over the coordinate-major sketch;
+ * from 8 tokens the pairs are grouped by expert and run on the tensor cores
+ * over the row-major sketch (when the layer has one).  Both give the same bits.
+ * Replaces: _sketch_screen and its helpers (progressive.py:478-1066),
+ * _group_sort (:2329-2382), _group_screen (:2428-2606). */
 int cfm_screen(const cfm_layer* layer, void* workspace, int32_t capacity,
                const cfm_call* call, void* stream);
+
+/* Score: selection scores from the projections (zero for remote or padded
+ * slots).  Only needed when scores are exchanged between ranks before the
+ * selection; cfm_select computes them itself unless call->scores_ready.
+ * Replaces: _screen_score (progressive.py:1274-1353). */
+int cfm_score(const cfm_layer* layer, void* workspace, int32_t capacity,
+              const cfm_call* call, void* stream);
 
 /* Select: per token the F best scores, ties to the lower candidate index;
  * writes selected, candidate_ids, counts, starts, tile_starts and adds the
