@@ -180,3 +180,31 @@ def workspace_layout(layer: Layer, capacity: int) -> WorkspaceLayout:
     if code:
         raise ValueError(load().cfm_error_string(code).decode())
     return layout
+
+
+class StaticScreen(ctypes.Structure):
+    """`struct cfm_static_screen`."""
+
+    _fields_ = [
+        ("tokens", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("ids", ctypes.c_void_p),
+        ("quantized", ctypes.c_void_p),
+        ("coordinates", ctypes.c_void_p),
+        ("exponents", ctypes.c_void_p),
+        ("padding", ctypes.c_void_p),
+        ("partial", ctypes.c_void_p),
+    ]
+
+
+E_STATIC_CAPACITY = -5
+STATIC_PARTS_FLOATS = 1 << 20
+STATIC_MAX_PAIRS = 1024
+
+
+def screen_static():
+    """The `cfm_screen_static` entry point, bound on first use."""
+    function = load().cfm_screen_static
+    function.restype = ctypes.c_int
+    function.argtypes = [ctypes.POINTER(Layer), ctypes.POINTER(StaticScreen), ctypes.c_void_p]
+    return function

@@ -21,6 +21,8 @@
 
 #include "cfm_b200.h"
 
+#include <mutex>
+
 namespace cfm {
 
 // ---------------------------------------------------------------------------
@@ -1404,6 +1406,7 @@ const char* cfm_error_string(int code) {
     case CFM_E_SHAPE: return "a dimension violates the layer contract";
     case CFM_E_CAPACITY: return "token count outside the workspace capacity";
     case CFM_E_UNSUPPORTED: return "option not supported by this build";
+    case CFM_E_STATIC_CAPACITY: return "batch exceeds the library-owned scratch of cfm_screen_static";
     default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
   }
 }
@@ -1448,3 +1451,105 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Screen with library-owned scratch (no allocation by anyone at call time)
+// ---------------------------------------------------------------------------
+// Scratch of cfm_screen_static: the per-block products of the split screen and
+// its arrival counters.  The arrays live in the library image, so every GPU
+// that loads the library holds them (4 MiB + 4 KiB) until the process exits.
+// All calls on a device share them.
+static __device__ __align__(256) float g_static_parts[CFM_STATIC_PARTS_FLOATS];
+static __device__ __align__(256) unsigned int g_static_counters[CFM_STATIC_MAX_PAIRS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+struct StaticScratch {
+  float* parts;
+  unsigned int* counters;
+  bool ready;
+};
+StaticScratch g_scratch[kMaxDevices];
+std::mutex g_scratch_lock;
+
+// Resolves the device addresses of the two arrays for the current device.  In
+// host code the array names are only handles; kernels need the addresses
+// cudaGetSymbolAddress returns for the device that is current.
+int static_scratch(StaticScratch* out) {
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  if (device < 0 || device >= kMaxDevices) return CFM_E_UNSUPPORTED;
+  std::lock_guard<std::mutex> guard(g_scratch_lock);
+  StaticScratch& slot = g_scratch[device];
+  if (!slot.ready) {
+    void* parts = nullptr;
+    void* counters = nullptr;
+    err = cudaGetSymbolAddress(&parts, g_static_parts);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    err = cudaGetSymbolAddress(&counters, g_static_counters);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    slot.parts = static_cast<float*>(parts);
+    slot.counters = static_cast<unsigned int*>(counters);
+    slot.ready = true;
+  }
+  *out = slot;
+  return 0;
+}
+}  // namespace
+
+extern "C" int cfm_screen_static(const cfm_layer* layer, const cfm_static_screen* io,
+                                 void* stream) {
+  if (!layer || !io) return CFM_E_NULL;
+  if (!io->ids || !io->quantized || !io->coordinates || !io->exponents || !io->partial ||
+      !layer->sketch || !layer->statistics)
+    return CFM_E_NULL;
+  cfm_workspace_layout layout;
+  int rc = make_layout(layer, 1, &layout);  // validates the dimensions
+  if (rc) return rc;
+  const Layer L = device_layer(layer);
+  if (L.F >= L.N) return CFM_E_SHAPE;  // unscreened plans have no screen
+  if (L.W > 512) return CFM_E_SHAPE;
+  if (io->tokens < 1) return CFM_E_CAPACITY;
+  const int64_t pairs = static_cast<int64_t>(io->tokens) * L.K;
+  if (pairs > CFM_STATIC_MAX_PAIRS ||
+      pairs * L.B * 2 * L.I > static_cast<int64_t>(CFM_STATIC_PARTS_FLOATS))
+    return CFM_E_STATIC_CAPACITY;
+  StaticScratch scratch;
+  if ((rc = static_scratch(&scratch))) return rc;
+
+  Workspace ws = {};
+  ws.ids = const_cast<int32_t*>(io->ids);
+  ws.quantized = const_cast<int32_t*>(io->quantized);
+  ws.coordinates = const_cast<int32_t*>(io->coordinates);
+  ws.exponents = const_cast<int32_t*>(io->exponents);
+  ws.parts = scratch.parts;
+  ws.counters = scratch.counters;
+  ws.partial = io->partial;
+  ws.parts_tokens = io->tokens;
+  ws.capacity = io->tokens;
+  Bound b;
+  b.L = L;
+  b.ws = ws;
+  b.stream = static_cast<cudaStream_t>(stream);
+  b.T = io->tokens;
+  b.padding = io->padding;
+  // The arrival counters must start at zero; the products need no clearing
+  // (every entry that is read has been written by this call).
+  const cudaError_t err = cudaMemsetAsync(scratch.counters, 0, sizeof(unsigned int) * pairs,
+                                          b.stream);
+  if (err != cudaSuccess) return static_cast<int>(err);
+  // Always split the rotation blocks across CTAs, so the scratch is what joins them.
+  int S = 2;
+  while (S < L.B && pairs * S < 2 * 148) S *= 2;
+  if (S > L.B) S = L.B;
+  if (L.B == 1) S = 1;
+  int cg = 4;
+  while (cg > 1 && L.W * cg > 512) cg >>= 1;
+  switch (cg) {
+    case 4: return launch_screen<4>(b, S);
+    case 2: return launch_screen<2>(b, S);
+    default: return launch_screen<1>(b, S);
+  }
+}
+

@@ -205,6 +205,45 @@ int cfm_output(const cfm_layer* layer, void* workspace, int32_t capacity,
 int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity,
                        const cfm_call* call, void* stream);
 
+/* ---- screen with library-owned scratch ----------------------------------- */
+#define CFM_E_STATIC_CAPACITY -5 /* batch beyond the library-owned scratch       */
+#define CFM_STATIC_PARTS_FLOATS (1 << 20) /* 4 MiB of per-block products          */
+#define CFM_STATIC_MAX_PAIRS 1024         /* (token, expert) pairs per call       */
+
+/* Inputs and output of cfm_screen_static: arrays in the formats cfm_route and
+ * cfm_prepare_input write (a caller may point into its own workspace). */
+typedef struct cfm_static_screen {
+  int32_t tokens;             /* T >= 1                                         */
+  int32_t reserved;
+  const int32_t* ids;         /* i32 [T, K] local expert ids, ascending per token */
+  const int32_t* quantized;   /* i32 [T, B, KEEP] fixed-point kept values        */
+  const int32_t* coordinates; /* i32 [T, B, KEEP] their coordinates              */
+  const int32_t* exponents;   /* i32 [T, B, 2] exponent and sum per block        */
+  const uint8_t* padding;     /* bool [T] or NULL                                */
+  float* partial;             /* out: f32 [T, 2, N] sketch projections           */
+} cfm_static_screen;
+
+/* The split screen (one GEMV per (token, expert) pair, rotation blocks spread
+ * over CTAs) for callers that cannot provide scratch memory of their own and
+ * must not cause an allocation: a decode step inside a serving engine that has
+ * already handed all free device memory to its cache pool, or a host plugin
+ * whose contract forbids touching the allocator.  The per-block products and
+ * the arrival counters that join the CTAs live in two arrays inside the library
+ * image (4 MiB + 4 KiB on every GPU that loads the library, held until exit);
+ * this function, and everything it calls, allocates nothing.
+ *
+ * Limits: T * K <= CFM_STATIC_MAX_PAIRS and T * K * B * 2I <=
+ * CFM_STATIC_PARTS_FLOATS, else CFM_E_STATIC_CAPACITY and nothing is launched.
+ * The first call on a device looks up the arrays' device addresses; make that
+ * call once, with the device current, before any stream capture begins.  All
+ * calls on a device share the arrays, which keep the previous call's contents:
+ * the counters are cleared on the stream at the start of every call, and two
+ * calls whose kernels overlap on the GPU (different streams) race.
+ * Results equal cfm_screen's bit for bit.
+ * No counterpart in the reference, whose scratch is always caller-allocated
+ * (ReaderWorkspace). */
+int cfm_screen_static(const cfm_layer* layer, const cfm_static_screen* io, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,81 @@
+"""The screen entry point that brings its own scratch (`cfm_screen_static`).
+
+Some callers of the reader cannot hand it scratch memory and must not trigger a
+device allocation: a decode step running inside a serving engine that has
+already given all free device memory to its cache pool, or a plugin host that
+forbids allocator calls.  For them the library keeps the split screen's scratch
+(per-block products and arrival counters) in two arrays of its own image.  This
+test calls that entry point through the C ABI, twice in a row on the same
+inputs, and requires both results to equal the regular `cfm_screen` output bit
+for bit (the bar of the other parity tests); the second call proves that what
+the first left in the shared arrays does not leak into the next result.
+
+Collected last on purpose, so a run that stops at the first failure has already
+covered every other test.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+from cfm_b200 import _native
+from helpers import prepared
+from test_gpu_parity import make_reader, run_reader
+
+pytestmark = pytest.mark.gpu
+
+
+def call_static(reader, tokens, out, padding=None):
+    w = reader.workspace
+    io = _native.StaticScreen()
+    io.tokens = tokens
+    io.ids = w.ids.data_ptr()
+    io.quantized = w.quantized.data_ptr()
+    io.coordinates = w.coordinates.data_ptr()
+    io.exponents = w.exponents.data_ptr()
+    io.padding = padding.data_ptr() if padding is not None else None
+    io.partial = out.data_ptr()
+    stream = torch.cuda.current_stream().cuda_stream
+    return _native.screen_static()(
+        ctypes.byref(reader._layer), ctypes.byref(io), ctypes.c_void_p(stream)
+    )
+
+
+def test_static_scratch_screen_matches_regular_screen_twice():
+    item = prepared("qwen35-e16-t4")
+    reader = make_reader(item)
+    run_reader(reader, item["case"])  # regular path: fills ids, kept values and `partial`
+    tokens = item["case"].hidden.shape[0]
+    expected = reader.partial[:tokens].clone()
+    assert torch.isfinite(expected).all() and expected.abs().sum() > 0
+    for _ in range(2):
+        out = torch.full_like(expected, float("nan"))
+        assert call_static(reader, tokens, out) == 0
+        torch.cuda.synchronize()
+        assert torch.equal(out, expected)
+
+
+def test_static_scratch_screen_with_padding_row():
+    item = prepared("graph-routes")  # second row is padding
+    reader = make_reader(item)
+    run_reader(reader, item["case"])
+    padding = item["case"].padding.cuda()
+    expected = reader.partial[:2].clone()
+    out = torch.full_like(expected, float("nan"))
+    assert call_static(reader, 2, out, padding) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out[0], expected[0])
+    assert not out[1].any()  # padded rows are written as zeros
+
+
+def test_static_scratch_screen_rejects_batches_beyond_its_arrays():
+    item = prepared("qwen3-e16-t8")  # 64 pairs x 16 blocks x 1536 rows > 2**20 floats
+    reader = make_reader(item)
+    run_reader(reader, item["case"])
+    out = torch.zeros_like(reader.partial[:8])
+    code = call_static(reader, 8, out)
+    assert code == _native.E_STATIC_CAPACITY
+    message = _native.load().cfm_error_string(code).decode()
+    assert "scratch" in message
+    assert not out.any()  # nothing was launched
