@@ -19,7 +19,7 @@ constexpr int kBlock = 128;          // coordinates per rotation block
 constexpr int kWordRows = 16;        // sketch rows per 32-bit word
 constexpr int kQuantBits = 21;       // block maximum maps into [2^21, 2^22]
 constexpr int kDownTileRows = 128;   // kept rows per down tile
-constexpr int kEncodeTileRows = 64;  // channels per encoder tile
+constexpr int kEncodeTileRows = 256; // channels per encoder tile
 constexpr unsigned kFull = 0xffffffffu;
 
 // Round an FP32 value to BF16 (nearest even) and widen it again.
@@ -94,7 +94,7 @@ __device__ __forceinline__ float point_score(float g, float u, float norm, float
 // 16-byte read-only load that does not allocate in L1 (streamed weights).
 __device__ __forceinline__ uint4 load_stream16(const void* p) {
   uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
@@ -102,7 +102,7 @@ __device__ __forceinline__ uint4 load_stream16(const void* p) {
 
 __device__ __forceinline__ uint32_t load_stream4(const void* p) {
   uint32_t v;
-  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  asm("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
 

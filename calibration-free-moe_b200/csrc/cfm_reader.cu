@@ -542,8 +542,7 @@ __device__ __forceinline__ void decode_word(uint32_t w, uint32_t& c0, uint32_t& 
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                        uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -552,163 +551,121 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 constexpr int kGroupWarps = 8;                   // 16 sketch rows per warp
 constexpr int kGroupRows = kGroupWarps * 16;     // rows per CTA
 constexpr int kGroupThreads = kGroupWarps * 32;
-constexpr int kLimbBlock = 3 * kBlock + 8;       // bytes of one (token, block) in shared memory
-constexpr int kPrefetch = 4;                     // rotation blocks of sketch words in flight
 
-// Bytes between token slots in shared memory: B blocks, padded so that the
-// stride in 32-bit words is 2 modulo 32 (conflict-free 8-byte fragment loads).
-__host__ __device__ inline int limb_slot_stride(int B) {
-  const int words = B * kLimbBlock / 4;
-  return (words + ((2 - words % 32) + 32) % 32) * 4;
+// m16n8k32 int8 MMA whose accumulator starts at zero.
+__device__ __forceinline__ void mma_s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                             uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// grid (ceil(2I / 128), E), 256 threads, dynamic shared memory
-// 8 NT * (limb_slot_stride(B) + 4 B) + 32 NT bytes.  A CTA owns 128 sketch rows
-// of one expert.  It first stages the int8 digits of all rotation blocks of up
-// to 8 NT of the expert's tokens in shared memory; then every warp walks the
-// rotation blocks in order on its own (no CTA barrier): it decodes its 16 rows
-// x 128 coordinates into int8 fragments and multiplies them with the digits
-// (m16n8k32, exact int32 sums), keeping sketch words of the next blocks in
-// flight in registers.  Token slot n * 8 + j of a pass is column j of tile n.
-template <int NT>
-__global__ void __launch_bounds__(kGroupThreads) k_screen_grouped(Layer L, Workspace ws) {
-  constexpr int kSlots = NT * 8;
-  extern __shared__ __align__(16) int8_t group_shared[];
-  const int stride = limb_slot_stride(L.B);
-  int8_t* limb_smem = group_shared;                                             // [kSlots][stride]
-  int* exponent_smem = reinterpret_cast<int*>(group_shared + kSlots * stride);  // [kSlots][B]
-  int* pair_smem = exponent_smem + kSlots * L.B;                                // [kSlots]
+// Everything a lane needs for one rotation block, fetched one block ahead.
+struct GroupFetch {
+  uint2 word_a, word_b;  // 32 coordinates of rows g and g + 8
+  uint4 digit[3][2];     // this lane's 32 coordinates of the three digits of token g
+  __half scale_a, scale_b;
+  int exponent[2];       // of the two tokens this lane finishes (2 tq, 2 tq + 1)
+};
+
+// grid (ceil(2I / 128), E), 256 threads, no shared memory, no barrier.  A warp
+// owns 16 sketch rows of one expert and walks the rotation blocks in order.  Per
+// block it decodes 16 rows x 128 coordinates into int8 fragments and multiplies
+// them with the int8 digits of up to eight of the expert's tokens (m16n8k32,
+// exact int32 sums; one 8-column tile per digit).  Lane (g, tq) holds
+// coordinates 32 tq .. 32 tq + 31 of rows g and g + 8 and of token g's digits,
+// so k-step m uses coordinates 32 tq + 8 m .. + 7 of all of them; the digits
+// come straight from global memory (L1/L2 resident, 32 contiguous bytes per
+// lane and digit).  The next block's words, digits, scales and exponents are
+// in flight in registers while the current block computes.  Experts with more
+// than eight tokens take further passes of eight.
+__global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Workspace ws) {
   const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int first = ws.group_offsets[e], total = ws.group_offsets[e + 1] - first;
-  if (total == 0) return;
   const int rows = 2 * L.I;
   const int r0 = blockIdx.x * kGroupRows + warp * 16;
-  const bool live = r0 < rows;  // whole warps are in or out: 2I is a multiple of 32
+  if (total == 0 || r0 >= rows) return;  // whole warps are in or out: 2I is a multiple of 32
   const int row_a = r0 + g, row_b = r0 + g + 8;
-  constexpr int kPieces = 3 * kBlock / 16;  // 16-byte pieces of one (token, block)
+  const uint2* sketch = reinterpret_cast<const uint2*>(L.sketch_grouped) + tq;
+  const size_t sketch_block = static_cast<size_t>(rows) * (kBlock / 32);  // uint2 per block
+  const size_t sketch_a = (static_cast<size_t>(e) * L.B * rows + row_a) * (kBlock / 32);
+  const size_t sketch_b = (static_cast<size_t>(e) * L.B * rows + row_b) * (kBlock / 32);
+  const __half* scales = L.statistics + static_cast<size_t>(e) * L.B * 2 * rows;
 
-  for (int base = 0; base < total; base += kSlots) {
-    const int count = min(kSlots, total - base);
-    __syncthreads();
-    if (tid < kSlots) pair_smem[tid] = tid < count ? ws.group_pairs[first + base + tid] : -1;
-    __syncthreads();
-    // Stage digits and exponents of every block of this pass's tokens.
-    const int pieces = kSlots * L.B * kPieces;
-    for (int index = tid; index < pieces; index += kGroupThreads) {
-      const int slot = index / (L.B * kPieces);
-      const int rest = index - slot * L.B * kPieces;
-      const int b = rest / kPieces, piece = rest - b * kPieces;
-      const int pair = pair_smem[slot];
-      uint4 digits = make_uint4(0, 0, 0, 0);
-      if (pair >= 0) {
-        const size_t tb = static_cast<size_t>(pair / L.K) * L.B + b;
-        digits = *reinterpret_cast<const uint4*>(ws.limbs + tb * 3 * kBlock + piece * 16);
+  for (int base = 0; base < total; base += 8) {
+    const int count = min(8, total - base);
+    // Pair of the token whose digits this lane feeds (column g of the tiles).
+    const int pair_g = g < count ? ws.group_pairs[first + base + g] : -1;
+    // Pairs of the two tokens whose results this lane finishes.
+    const int pair_0 = __shfl_sync(kFull, pair_g, (2 * tq) * 4);
+    const int pair_1 = __shfl_sync(kFull, pair_g, (2 * tq + 1) * 4);
+    const int token_g = pair_g >= 0 ? pair_g / L.K : -1;
+    const int token_0 = pair_0 >= 0 ? pair_0 / L.K : -1;
+    const int token_1 = pair_1 >= 0 ? pair_1 / L.K : -1;
+    const int8_t* digits =
+        ws.limbs + static_cast<size_t>(max(token_g, 0)) * L.B * 3 * kBlock + 32 * tq;
+
+    auto fetch = [&](int b) {
+      GroupFetch f;
+      f.word_a = sketch[sketch_a + b * sketch_block];
+      f.word_b = sketch[sketch_b + b * sketch_block];
+      f.scale_a = scales[static_cast<size_t>(b) * 2 * rows + row_a];
+      f.scale_b = scales[static_cast<size_t>(b) * 2 * rows + row_b];
+#pragma unroll
+      for (int j = 0; j < 3; ++j) {
+        f.digit[j][0] = f.digit[j][1] = make_uint4(0, 0, 0, 0);
+        if (token_g >= 0) {
+          const uint4* p = reinterpret_cast<const uint4*>(digits + (b * 3 + j) * kBlock);
+          f.digit[j][0] = p[0];
+          f.digit[j][1] = p[1];
+        }
       }
-      int8_t* dst = limb_smem + slot * stride + b * kLimbBlock + piece * 16;
-      *reinterpret_cast<uint2*>(dst) = make_uint2(digits.x, digits.y);
-      *reinterpret_cast<uint2*>(dst + 8) = make_uint2(digits.z, digits.w);
-    }
-    for (int index = tid; index < kSlots * L.B; index += kGroupThreads) {
-      const int slot = index / L.B, b = index - slot * L.B;
-      const int pair = pair_smem[slot];
-      exponent_smem[index] =
-          pair >= 0 ? ws.exponents[2 * (static_cast<size_t>(pair / L.K) * L.B + b)] : 0;
-    }
-    __syncthreads();
-    if (!live) continue;
-
-    auto sketch_at = [&](int b, int row) {
-      return reinterpret_cast<const uint2*>(
-                 L.sketch_grouped +
-                 ((static_cast<size_t>(e) * L.B + b) * rows + row) * (kBlock / 16)) + tq;
+      f.exponent[0] = token_0 >= 0 ? ws.exponents[2 * (static_cast<size_t>(token_0) * L.B + b)]
+                                   : kQuantBits;
+      f.exponent[1] = token_1 >= 0 ? ws.exponents[2 * (static_cast<size_t>(token_1) * L.B + b)]
+                                   : kQuantBits;
+      return f;
     };
-    auto scale_at = [&](int b, int row) {
-      return L.statistics[(static_cast<size_t>(e) * L.B + b) * 2 * rows + row];
-    };
-    uint2 word_a[kPrefetch], word_b[kPrefetch];
-    __half scale_a[kPrefetch], scale_b[kPrefetch];
-#pragma unroll
-    for (int u = 0; u < kPrefetch; ++u) {
-      if (u < L.B) {
-        word_a[u] = *sketch_at(u, row_a);
-        word_b[u] = *sketch_at(u, row_b);
-        scale_a[u] = scale_at(u, row_a);
-        scale_b[u] = scale_at(u, row_b);
-      }
-    }
-    float run[NT][4];
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) run[n][i] = 0.0f;
 
-    for (int b0 = 0; b0 < L.B; b0 += kPrefetch) {
+    float run[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    GroupFetch next = fetch(0);
+    for (int b = 0; b < L.B; ++b) {
+      const GroupFetch cur = next;
+      if (b + 1 < L.B) next = fetch(b + 1);
+      uint32_t fa[8], fb[8];
+      decode_word(cur.word_a.x, fa[0], fa[1], fa[2], fa[3]);
+      decode_word(cur.word_a.y, fa[4], fa[5], fa[6], fa[7]);
+      decode_word(cur.word_b.x, fb[0], fb[1], fb[2], fb[3]);
+      decode_word(cur.word_b.y, fb[4], fb[5], fb[6], fb[7]);
+      int acc[3][4];
 #pragma unroll
-      for (int u = 0; u < kPrefetch; ++u) {
-        const int b = b0 + u;
-        if (b >= L.B) break;
-        const uint2 cur_a = word_a[u], cur_b = word_b[u];
-        const float cur_scale_a = __half2float(scale_a[u]), cur_scale_b = __half2float(scale_b[u]);
-        if (b + kPrefetch < L.B) {
-          word_a[u] = *sketch_at(b + kPrefetch, row_a);
-          word_b[u] = *sketch_at(b + kPrefetch, row_b);
-          scale_a[u] = scale_at(b + kPrefetch, row_a);
-          scale_b[u] = scale_at(b + kPrefetch, row_b);
-        }
-        int acc[NT][3][4];
-#pragma unroll
-        for (int n = 0; n < NT; ++n)
-#pragma unroll
-          for (int j = 0; j < 3; ++j)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) acc[n][j][i] = 0;
-        // Thread (g, tq) holds coordinates 32 tq .. 32 tq + 31 of rows g and g+8:
-        // k-step m uses coordinates 32 tq + 8 m .. + 7.
-        uint32_t fa[8], fb[8];
-        decode_word(cur_a.x, fa[0], fa[1], fa[2], fa[3]);
-        decode_word(cur_a.y, fa[4], fa[5], fa[6], fa[7]);
-        decode_word(cur_b.x, fb[0], fb[1], fb[2], fb[3]);
-        decode_word(cur_b.y, fb[4], fb[5], fb[6], fb[7]);
-        const int8_t* limbs = limb_smem + b * kLimbBlock + 32 * tq;
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-#pragma unroll
-          for (int n = 0; n < NT; ++n) {
-#pragma unroll
-            for (int j = 0; j < 3; ++j) {
-              const uint2 bv = *reinterpret_cast<const uint2*>(
-                  limbs + (n * 8 + g) * stride + j * kBlock + 8 * m);
-              mma_s8(acc[n][j], fa[2 * m], fb[2 * m], fa[2 * m + 1], fb[2 * m + 1], bv.x, bv.y);
-            }
-          }
-        }
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int dot = acc[n][0][i] + acc[n][1][i] * 256 + acc[n][2][i] * 65536;
-            const int be = exponent_smem[(n * 8 + 2 * tq + (i & 1)) * L.B + b];
-            const float unscale =
-                __uint_as_float(static_cast<uint32_t>(127 + be - kQuantBits) << 23);
-            const float d = __fmul_rn(__int2float_rn(dot), unscale);
-            const float prod = __fmul_rn(i < 2 ? cur_scale_a : cur_scale_b, d);
-            run[n][i] = __fadd_rn(run[n][i], prod);
-          }
-        }
+      for (int j = 0; j < 3; ++j) {
+        const uint4 lo = cur.digit[j][0], hi = cur.digit[j][1];
+        mma_s8_first(acc[j], fa[0], fb[0], fa[1], fb[1], lo.x, lo.y);
+        mma_s8(acc[j], fa[2], fb[2], fa[3], fb[3], lo.z, lo.w);
+        mma_s8(acc[j], fa[4], fb[4], fa[5], fb[5], hi.x, hi.y);
+        mma_s8(acc[j], fa[6], fb[6], fa[7], fb[7], hi.z, hi.w);
       }
-    }
-#pragma unroll
-    for (int n = 0; n < NT; ++n) {
+      const float scale_a = __half2float(cur.scale_a), scale_b = __half2float(cur.scale_b);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int pair = pair_smem[n * 8 + 2 * tq + (i & 1)];
-        if (pair < 0) continue;
-        const int row = (i < 2) ? row_a : row_b;
-        const int t = pair / L.K, slot = pair - t * L.K;
-        float* out = ws.partial + static_cast<size_t>(t) * 2 * L.N + static_cast<size_t>(slot) * L.I;
-        (row < L.I ? out[row] : out[L.N + row - L.I]) = run[n][i];
+        const int dot = acc[0][i] + acc[1][i] * 256 + acc[2][i] * 65536;
+        const float unscale = __uint_as_float(
+            static_cast<uint32_t>(127 + cur.exponent[i & 1] - kQuantBits) << 23);
+        const float d = __fmul_rn(__int2float_rn(dot), unscale);
+        run[i] = __fadd_rn(run[i], __fmul_rn(i < 2 ? scale_a : scale_b, d));
       }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int pair = (i & 1) ? pair_1 : pair_0;
+      if (pair < 0) continue;
+      const int row = (i < 2) ? row_a : row_b;
+      const int t = pair / L.K, slot = pair - t * L.K;
+      float* out = ws.partial + static_cast<size_t>(t) * 2 * L.N + static_cast<size_t>(slot) * L.I;
+      (row < L.I ? out[row] : out[L.N + row - L.I]) = run[i];
     }
   }
 }
@@ -753,7 +710,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
                                                            const uint8_t* padding,
                                                            int scores_ready) {
   extern __shared__ uint32_t keys[];
-  __shared__ int hist[256];
+  __shared__ int hist[2048];
   __shared__ int warp_above[32], warp_ties[32];
   __shared__ int s_digit, s_remaining;
   __shared__ int s_starts[33];
@@ -787,55 +744,56 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
         keys[i] = __float_as_uint(value);
       }
     }
-    // Radix search, most significant byte first, for the F-th largest key.
+    // Radix search for the F-th largest key: digits of 11, 11 and 10 bits from
+    // the top.  Each pass histograms the keys that match the prefix found so far,
+    // then a block-wide scan from the highest digit down locates the digit in
+    // which the running count reaches the number still wanted.
     uint32_t prefix = 0, mask = 0;
     int remaining = F;
-    for (int pass = 3; pass >= 0; --pass) {
-      if (tid < 256) hist[tid] = 0;
+#pragma unroll 1
+    for (int pass = 0; pass < 3; ++pass) {
+      const int shift = pass == 0 ? 21 : pass == 1 ? 10 : 0;
+      const int bins = pass == 2 ? 1024 : 2048;
+      for (int i = tid; i < bins; i += kSelectThreads) hist[i] = 0;
       __syncthreads();
-      const int shift = 8 * pass;
       for (int i = tid; i < N; i += kSelectThreads) {
         const uint32_t k = keys[i];
-        if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1);
+        if ((k & mask) == prefix) atomicAdd(&hist[(k >> shift) & (bins - 1)], 1);
       }
       __syncthreads();
-      if (warp == 0) {
-        // Suffix counts over the 256 digits, 8 per lane, from the top digit down.
-        int mine[8], total = 0;
+      // Thread tid owns digits bins-1-2*tid and bins-2-2*tid (descending order).
+      const int d0 = bins - 1 - 2 * tid;
+      const int c0 = d0 >= 0 ? hist[d0] : 0;
+      const int c1 = d0 >= 1 ? hist[d0 - 1] : 0;
+      const int total = c0 + c1;
+      int scan = total;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          mine[j] = hist[255 - (lane * 8 + j)];
-          total += mine[j];
-        }
-        int before = total;  // inclusive scan over lanes
+      for (int w = 1; w < 32; w <<= 1) {
+        const int o = __shfl_up_sync(kFull, scan, w);
+        if (lane >= w) scan += o;
+      }
+      if (lane == 31) warp_above[warp] = scan;
+      __syncthreads();
+      if (warp == 0) {
+        int totals = warp_above[lane];
 #pragma unroll
         for (int w = 1; w < 32; w <<= 1) {
-          const int o = __shfl_up_sync(kFull, before, w);
-          if (lane >= w) before += o;
+          const int o = __shfl_up_sync(kFull, totals, w);
+          if (lane >= w) totals += o;
         }
-        before -= total;  // keys in strictly higher digits than this lane's
-        int found = -1, above = 0;
-        if (before < remaining && before + total >= remaining) {
-          int cum = before;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (found < 0 && cum + mine[j] >= remaining) {
-              found = 255 - (lane * 8 + j);
-              above = cum;
-            }
-            cum += mine[j];
-          }
-        }
-        if (found >= 0) {
-          s_digit = found;
-          s_remaining = remaining - above;
-        }
+        warp_ties[lane] = totals;  // inclusive scan of the warp totals
+      }
+      __syncthreads();
+      const int before = scan - total + (warp ? warp_ties[warp - 1] : 0);
+      if (before < remaining && before + total >= remaining) {
+        const bool first = before + c0 >= remaining;
+        s_digit = first ? d0 : d0 - 1;
+        s_remaining = remaining - (first ? before : before + c0);
       }
       __syncthreads();
       prefix |= static_cast<uint32_t>(s_digit) << shift;
-      mask |= 255u << shift;
+      mask |= static_cast<uint32_t>(bins - 1) << shift;
       remaining = s_remaining;
-      __syncthreads();
     }
     cut = prefix;
     take_ties = remaining;
@@ -989,25 +947,48 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
       L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
   const uint4* up = gate + static_cast<size_t>(L.I) * L.H / 8;
   float g = 0.0f, u = 0.0f;
-#pragma unroll 4
-  for (int i = lane; i < chunks; i += 32) {
-    const uint4 gw = load_stream16(gate + i), uw = load_stream16(up + i), xw = xs[i];
-    g = fmaf(bf16_lo(gw.x), bf16_lo(xw.x), g);
-    g = fmaf(bf16_hi(gw.x), bf16_hi(xw.x), g);
-    g = fmaf(bf16_lo(gw.y), bf16_lo(xw.y), g);
-    g = fmaf(bf16_hi(gw.y), bf16_hi(xw.y), g);
-    g = fmaf(bf16_lo(gw.z), bf16_lo(xw.z), g);
-    g = fmaf(bf16_hi(gw.z), bf16_hi(xw.z), g);
-    g = fmaf(bf16_lo(gw.w), bf16_lo(xw.w), g);
-    g = fmaf(bf16_hi(gw.w), bf16_hi(xw.w), g);
-    u = fmaf(bf16_lo(uw.x), bf16_lo(xw.x), u);
-    u = fmaf(bf16_hi(uw.x), bf16_hi(xw.x), u);
-    u = fmaf(bf16_lo(uw.y), bf16_lo(xw.y), u);
-    u = fmaf(bf16_hi(uw.y), bf16_hi(xw.y), u);
-    u = fmaf(bf16_lo(uw.z), bf16_lo(xw.z), u);
-    u = fmaf(bf16_hi(uw.z), bf16_hi(xw.z), u);
-    u = fmaf(bf16_lo(uw.w), bf16_lo(xw.w), u);
-    u = fmaf(bf16_hi(uw.w), bf16_hi(xw.w), u);
+  // Eight 16-byte pieces of each row in flight per lane (2048 columns per sweep).
+  constexpr int U = 8;
+  for (int base = lane; base < chunks; base += 32 * U) {
+    uint4 gw[U], uw[U];
+    if (base + 32 * (U - 1) < chunks) {
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        gw[k] = load_stream16(gate + base + 32 * k);
+        uw[k] = load_stream16(up + base + 32 * k);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const int i = base + 32 * k;
+        gw[k] = uw[k] = make_uint4(0, 0, 0, 0);
+        if (i < chunks) {
+          gw[k] = load_stream16(gate + i);
+          uw[k] = load_stream16(up + i);
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const int i = min(base + 32 * k, chunks - 1);
+      const uint4 xw = xs[i];
+      g = fmaf(bf16_lo(gw[k].x), bf16_lo(xw.x), g);
+      g = fmaf(bf16_hi(gw[k].x), bf16_hi(xw.x), g);
+      g = fmaf(bf16_lo(gw[k].y), bf16_lo(xw.y), g);
+      g = fmaf(bf16_hi(gw[k].y), bf16_hi(xw.y), g);
+      g = fmaf(bf16_lo(gw[k].z), bf16_lo(xw.z), g);
+      g = fmaf(bf16_hi(gw[k].z), bf16_hi(xw.z), g);
+      g = fmaf(bf16_lo(gw[k].w), bf16_lo(xw.w), g);
+      g = fmaf(bf16_hi(gw[k].w), bf16_hi(xw.w), g);
+      u = fmaf(bf16_lo(uw[k].x), bf16_lo(xw.x), u);
+      u = fmaf(bf16_hi(uw[k].x), bf16_hi(xw.x), u);
+      u = fmaf(bf16_lo(uw[k].y), bf16_lo(xw.y), u);
+      u = fmaf(bf16_hi(uw[k].y), bf16_hi(xw.y), u);
+      u = fmaf(bf16_lo(uw[k].z), bf16_lo(xw.z), u);
+      u = fmaf(bf16_hi(uw[k].z), bf16_hi(xw.z), u);
+      u = fmaf(bf16_lo(uw[k].w), bf16_lo(xw.w), u);
+      u = fmaf(bf16_hi(uw[k].w), bf16_hi(xw.w), u);
+    }
   }
 #pragma unroll
   for (int w = 16; w; w >>= 1) {
@@ -1047,25 +1028,54 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
   const int32_t* list =
       ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[static_cast<size_t>(t) * L.K + slot] + first;
   const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
+  // Stage the tile's channels and activations, then stream the rows.
+  __shared__ int tile_channel[kDownTileRows];
+  __shared__ float tile_activation[kDownTileRows];
+  if (tid < rows) {
+    const int cid = list[tid];
+    tile_channel[tid] = cid - slot * L.I;
+    tile_activation[tid] = __bfloat162float(act[cid]);
+  }
+  __syncthreads();
   const int group = tid >> 4, col = (tid & 15) * 8 + blockIdx.x * 128;
   const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + col;
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-#pragma unroll 4
-  for (int r = group; r < rows; r += 8) {
-    const int cid = list[r];
-    const int c = cid - slot * L.I;
-    const float a = __bfloat162float(act[cid]);
-    const uint4 w = load_stream16(base + static_cast<size_t>(c) * L.H);
-    acc[0] = fmaf(bf16_lo(w.x), a, acc[0]);
-    acc[1] = fmaf(bf16_hi(w.x), a, acc[1]);
-    acc[2] = fmaf(bf16_lo(w.y), a, acc[2]);
-    acc[3] = fmaf(bf16_hi(w.y), a, acc[3]);
-    acc[4] = fmaf(bf16_lo(w.z), a, acc[4]);
-    acc[5] = fmaf(bf16_hi(w.z), a, acc[5]);
-    acc[6] = fmaf(bf16_lo(w.w), a, acc[6]);
-    acc[7] = fmaf(bf16_hi(w.w), a, acc[7]);
+  constexpr int U = 8;  // rows in flight per thread
+  for (int r0 = group; r0 < rows; r0 += 8 * U) {
+    uint4 w[U];
+    float a[U];
+    if (r0 + 8 * (U - 1) < rows) {
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const int r = r0 + 8 * k;
+        w[k] = load_stream16(base + static_cast<size_t>(tile_channel[r]) * L.H);
+        a[k] = tile_activation[r];
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const int r = r0 + 8 * k;
+        w[k] = make_uint4(0, 0, 0, 0);
+        a[k] = 0.0f;
+        if (r < rows) {
+          w[k] = load_stream16(base + static_cast<size_t>(tile_channel[r]) * L.H);
+          a[k] = tile_activation[r];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      acc[0] = fmaf(bf16_lo(w[k].x), a[k], acc[0]);
+      acc[1] = fmaf(bf16_hi(w[k].x), a[k], acc[1]);
+      acc[2] = fmaf(bf16_lo(w[k].y), a[k], acc[2]);
+      acc[3] = fmaf(bf16_hi(w[k].y), a[k], acc[3]);
+      acc[4] = fmaf(bf16_lo(w[k].z), a[k], acc[4]);
+      acc[5] = fmaf(bf16_hi(w[k].z), a[k], acc[5]);
+      acc[6] = fmaf(bf16_lo(w[k].w), a[k], acc[6]);
+      acc[7] = fmaf(bf16_hi(w[k].w), a[k], acc[7]);
+    }
   }
   __shared__ float red[8][128];
 #pragma unroll
@@ -1080,16 +1090,26 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
 // ---------------------------------------------------------------------------
 // encode: recovery encoder over skipped channels, then the latent
 // ---------------------------------------------------------------------------
-// grid (encoder_tiles, T*K), 128 threads.  LPR = R / 8 lanes cover one encoder
-// row (16 bytes each); 128 / LPR row groups walk the tile's 64 channels.
-__global__ void __launch_bounds__(128) k_encode(Layer L, Workspace ws, const uint8_t* padding) {
-  __shared__ float red[128 * 8];
+// grid (encoder_tiles, T*K), 256 threads.  A CTA owns 256 channels of one
+// (token, expert) pair.  Phase 1 turns the sketch projections of the skipped
+// channels into features in shared memory (0 for kept channels); phase 2
+// streams the encoder rows: LPR = R / 8 lanes cover one row (16 bytes each),
+// 256 / LPR row groups walk the channels with eight rows in flight per thread;
+// phase 3 folds the row groups (shuffles inside a warp, shared memory across
+// warps).  The last CTA of a token to arrive mixes the latent.
+constexpr int kEncodeThreads = 256;
+
+__global__ void __launch_bounds__(kEncodeThreads) k_encode(Layer L, Workspace ws,
+                                                           const uint8_t* padding) {
+  __shared__ float feature[kEncodeTileRows];
+  __shared__ float red[kEncodeThreads / 32][256];
   __shared__ int s_last;
   const int tile = blockIdx.x, pair = blockIdx.y, tid = threadIdx.x;
   const int t = pair / L.K, slot = pair - t * L.K;
-  const int R = L.R, lpr = R / 8, groups = 128 / lpr;
+  const int R = L.R, lpr = R / 8, groups = kEncodeThreads / lpr;
   const int e = ws.ids[pair];
   const bool dead = (padding && padding[t]) || e < 0;
+  const int c0 = tile * kEncodeTileRows, c1 = min(L.I, c0 + kEncodeTileRows);
   const int group = tid / lpr, col = (tid - group * lpr) * 8;
   float acc[8];
 #pragma unroll
@@ -1098,32 +1118,67 @@ __global__ void __launch_bounds__(128) k_encode(Layer L, Workspace ws, const uin
     const float* pg = ws.partial + static_cast<size_t>(t) * 2 * L.N + slot * L.I;
     const float* pu = pg + L.N;
     const uint8_t* sel = ws.selected + static_cast<size_t>(t) * L.N + slot * L.I;
+    for (int c = c0 + tid; c < c1; c += kEncodeThreads)
+      feature[c - c0] = sel[c] ? 0.0f : sketch_feature(pg[c], pu[c], L.activation);
+    __syncthreads();
     const __nv_bfloat16* enc = L.encoder + static_cast<size_t>(e) * L.I * R + col;
-    const int c1 = min(L.I, (tile + 1) * kEncodeTileRows);
-#pragma unroll 2
-    for (int c = tile * kEncodeTileRows + group; c < c1; c += groups) {
-      if (sel[c]) continue;
-      const float p = sketch_feature(pg[c], pu[c], L.activation);
-      const uint4 w = *reinterpret_cast<const uint4*>(enc + static_cast<size_t>(c) * R);
-      acc[0] = fmaf(bf16_lo(w.x), p, acc[0]);
-      acc[1] = fmaf(bf16_hi(w.x), p, acc[1]);
-      acc[2] = fmaf(bf16_lo(w.y), p, acc[2]);
-      acc[3] = fmaf(bf16_hi(w.y), p, acc[3]);
-      acc[4] = fmaf(bf16_lo(w.z), p, acc[4]);
-      acc[5] = fmaf(bf16_hi(w.z), p, acc[5]);
-      acc[6] = fmaf(bf16_lo(w.w), p, acc[6]);
-      acc[7] = fmaf(bf16_hi(w.w), p, acc[7]);
+    constexpr int U = 8;
+    for (int base = c0 + group; base < c1; base += groups * U) {
+      uint4 w[U];
+      float p[U];
+      if (base + (U - 1) * groups < c1) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int c = base + u * groups;
+          p[u] = feature[c - c0];
+          w[u] = *reinterpret_cast<const uint4*>(enc + static_cast<size_t>(c) * R);
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int c = base + u * groups;
+          p[u] = 0.0f;
+          w[u] = make_uint4(0, 0, 0, 0);
+          if (c < c1) {
+            p[u] = feature[c - c0];
+            w[u] = *reinterpret_cast<const uint4*>(enc + static_cast<size_t>(c) * R);
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        acc[0] = fmaf(bf16_lo(w[u].x), p[u], acc[0]);
+        acc[1] = fmaf(bf16_hi(w[u].x), p[u], acc[1]);
+        acc[2] = fmaf(bf16_lo(w[u].y), p[u], acc[2]);
+        acc[3] = fmaf(bf16_hi(w[u].y), p[u], acc[3]);
+        acc[4] = fmaf(bf16_lo(w[u].z), p[u], acc[4]);
+        acc[5] = fmaf(bf16_hi(w[u].z), p[u], acc[5]);
+        acc[6] = fmaf(bf16_lo(w[u].w), p[u], acc[6]);
+        acc[7] = fmaf(bf16_hi(w[u].w), p[u], acc[7]);
+      }
     }
   }
-  // red[group][R]
+  // Fold the row groups that share a warp (lanes lpr apart hold the same columns).
+  for (int w = lpr; w < 32; w <<= 1) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) red[group * R + col + j] = acc[j];
+    for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(kFull, acc[j], w);
+  }
+  const int lane = tid & 31, warp = tid >> 5;
+  if (lpr >= 32) {
+    // One row spans the whole warp or more: lane owns columns (tid % lpr) * 8.
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[group][col + j] = acc[j];
+  } else if (lane < lpr) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[warp][col + j] = acc[j];
+  }
   __syncthreads();
+  const int folds = lpr >= 32 ? groups : kEncodeThreads / 32;
   float* parts = ws.encoder_parts + (static_cast<size_t>(pair) * ws.encoder_tiles + tile) * R;
-  for (int r = tid; r < R; r += 128) {
-    float s = 0.0f;
-    for (int g = 0; g < groups; ++g) s += red[g * R + r];
-    parts[r] = s;
+  for (int r = tid; r < R; r += kEncodeThreads) {
+    float sum = 0.0f;
+    for (int f = 0; f < folds; ++f) sum += red[f][r];
+    parts[r] = sum;
   }
   // Last CTA of the token mixes the latent.
   __threadfence();
@@ -1138,16 +1193,16 @@ __global__ void __launch_bounds__(128) k_encode(Layer L, Workspace ws, const uin
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  for (int r = tid; r < R; r += 128) {
+  for (int r = tid; r < R; r += kEncodeThreads) {
     float latent = 0.0f;
-    for (int s = 0; s < L.K; ++s) {
-      const int pe = ws.ids[static_cast<size_t>(t) * L.K + s];
+    for (int s2 = 0; s2 < L.K; ++s2) {
+      const int pe = ws.ids[static_cast<size_t>(t) * L.K + s2];
       if (pe < 0 || (padding && padding[t])) continue;
       const float* p = ws.encoder_parts +
-                       (static_cast<size_t>(t) * L.K + s) * ws.encoder_tiles * R + r;
+                       (static_cast<size_t>(t) * L.K + s2) * ws.encoder_tiles * R + r;
       float sum = 0.0f;
       for (int j = 0; j < ws.encoder_tiles; ++j) sum += __ldcg(p + static_cast<size_t>(j) * R);
-      latent = fmaf(bf16_round(sum), ws.weights[static_cast<size_t>(t) * L.K + s], latent);
+      latent = fmaf(bf16_round(sum), ws.weights[static_cast<size_t>(t) * L.K + s2], latent);
     }
     ws.latent[static_cast<size_t>(t) * R + r] = latent;
   }
@@ -1282,26 +1337,7 @@ static int run_screen_grouped(const Bound& b) {
   int rc = launched();
   if (rc) return rc;
   const dim3 grid((2 * b.L.I + kGroupRows - 1) / kGroupRows, b.L.E);
-  // Two tiles of eight tokens per pass once experts hold more than six pairs on
-  // average and the digits of sixteen tokens still fit in shared memory.
-  const auto shared = [&](int slots) {
-    return static_cast<size_t>(slots) * (limb_slot_stride(b.L.B) + 4 * b.L.B) + 4 * slots;
-  };
-  const bool wide = static_cast<int64_t>(b.T) * b.L.K > 6LL * b.L.E && shared(16) <= 100 * 1024;
-  const size_t smem = shared(wide ? 16 : 8);
-  if (smem > 200 * 1024) return CFM_E_SHAPE;  // H beyond 128 * 64
-  const void* kernel = wide ? reinterpret_cast<const void*>(k_screen_grouped<2>)
-                            : reinterpret_cast<const void*>(k_screen_grouped<1>);
-  if (smem > 48 * 1024) {
-    const cudaError_t err = cudaFuncSetAttribute(
-        kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    if (err != cudaSuccess) return static_cast<int>(err);
-  }
-  if (wide) {
-    k_screen_grouped<2><<<grid, kGroupThreads, smem, b.stream>>>(b.L, b.ws);
-  } else {
-    k_screen_grouped<1><<<grid, kGroupThreads, smem, b.stream>>>(b.L, b.ws);
-  }
+  k_screen_grouped<<<grid, kGroupThreads, 0, b.stream>>>(b.L, b.ws);
   if ((rc = launched())) return rc;
   if (b.padding || b.L.expert_map) {
     k_clear_dead<<<dim3(b.T, (b.L.N + 255) / 256), 256, 0, b.stream>>>(b.L, b.ws, b.padding);
@@ -1338,7 +1374,7 @@ static int run_screen(const Bound& b) {
 
 static int run_select(const Bound& b, int scores_ready) {
   const size_t smem = sizeof(uint32_t) * b.L.N;
-  if (smem + 2048 > 48 * 1024) {  // static shared memory counts against the default limit
+  if (smem + 10240 > 48 * 1024) {  // static shared memory counts against the default limit
     const cudaError_t err = cudaFuncSetAttribute(
         k_select, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);
@@ -1377,7 +1413,7 @@ static int run_encode(const Bound& b) {
     k_zero_latent<<<b.T, 128, 0, b.stream>>>(b.L, b.ws);
     return launched();
   }
-  k_encode<<<dim3(b.ws.encoder_tiles, b.T * b.L.K), 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+  k_encode<<<dim3(b.ws.encoder_tiles, b.T * b.L.K), kEncodeThreads, 0, b.stream>>>(b.L, b.ws, b.padding);
   return launched();
 }
 
@@ -1386,6 +1422,39 @@ static int run_output(const Bound& b, const cfm_call* call) {
   k_output<<<dim3(b.L.H / 128, b.T), 128, 0, b.stream>>>(
       b.L, b.ws, b.padding, static_cast<__nv_bfloat16*>(call->out));
   return launched();
+}
+
+// One side stream and two events per device, created on the first whole-layer
+// call on that device (make that call outside stream capture).
+struct SideStream {
+  cudaStream_t stream;
+  cudaEvent_t fork, join;
+  bool ready;
+};
+static SideStream g_side[64];
+static std::mutex g_side_lock;
+
+static int side_stream(SideStream* out) {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return -1;
+  std::lock_guard<std::mutex> guard(g_side_lock);
+  SideStream& slot = g_side[device];
+  if (!slot.ready) {
+    int low = 0, high = 0;
+    if (cudaDeviceGetStreamPriorityRange(&low, &high) != cudaSuccess) return -1;
+    if (cudaStreamCreateWithPriority(&slot.stream, cudaStreamNonBlocking, high) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return -1;
+    }
+    if (cudaEventCreateWithFlags(&slot.fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&slot.join, cudaEventDisableTiming) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return -1;
+    }
+    slot.ready = true;
+  }
+  *out = slot;
+  return 0;
 }
 
 }  // namespace cfm
@@ -1444,9 +1513,27 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
   if ((rc = run_route(b, call))) return rc;
   if ((rc = run_screen(b))) return rc;
   if ((rc = run_select(b, 0))) return rc;
+  // The recovery encoder (L2-resident rows, arithmetic) runs beside the two
+  // HBM-bound gathers on a side stream and joins before the output mix.
+  SideStream side;
+  const bool fork = b.L.R > 0 && b.L.F < b.L.N && side_stream(&side) == 0;
+  if (fork) {
+    cudaError_t err = cudaEventRecord(side.fork, b.stream);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(side.stream, side.fork, 0);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    Bound on_side = b;
+    on_side.stream = side.stream;
+    if ((rc = run_encode(on_side))) return rc;
+    if ((err = cudaEventRecord(side.join, side.stream)) != cudaSuccess) return static_cast<int>(err);
+  }
   if ((rc = run_exact(b, call))) return rc;
   if ((rc = run_down(b))) return rc;
-  if ((rc = run_encode(b))) return rc;
+  if (fork) {
+    const cudaError_t err = cudaStreamWaitEvent(b.stream, side.join, 0);
+    if (err != cudaSuccess) return static_cast<int>(err);
+  } else if ((rc = run_encode(b))) {
+    return rc;
+  }
   return run_output(b, call);
 }
 

@@ -122,7 +122,7 @@ typedef struct cfm_workspace_layout {
   int64_t group_pairs;    /* i32 [C * K] (token, slot) pairs grouped by expert  */
   int32_t parts_tokens;   /* tokens the split screen can serve                  */
   int32_t down_tiles;     /* ceil(F / 128) + K - 1                              */
-  int32_t encoder_tiles;  /* ceil(I / 64)                                       */
+  int32_t encoder_tiles;  /* ceil(I / 256)                                      */
   int32_t reserved;
 } cfm_workspace_layout;
 
