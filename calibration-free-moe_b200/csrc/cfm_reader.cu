@@ -1006,64 +1006,63 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
 // ---------------------------------------------------------------------------
 // down: gathered channel-major down rows
 // ---------------------------------------------------------------------------
-// grid (H / 128, down_tiles, T), 128 threads = 8 row groups x 16 lanes of 8
-// columns.  One CTA sums up to 128 kept rows of one expert over 128 columns.
+// grid (ceil(H / COLS), down_tiles, T), 128 threads = GROUPS row groups x
+// 128 / GROUPS lanes of 8 columns, COLS = 1024 / GROUPS.  One CTA sums up to
+// 128 kept rows of one expert over COLS columns with eight 16-byte loads in
+// flight per thread.  GROUPS = 8 (128 columns per CTA) measured fastest at every
+// batch size on B200: it gives the most CTAs and the shortest per-thread chains.
+template <int GROUPS>
 __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8_t* padding) {
-  const int t = blockIdx.z, tile = blockIdx.y, tid = threadIdx.x;
-  if (padding && padding[t]) return;
-  const int32_t* tile_starts = ws.tile_starts + static_cast<size_t>(t) * L.K;
-  const int32_t* counts = ws.counts + static_cast<size_t>(t) * L.K;
-  int slot = -1, first = 0;
-  for (int s = 0; s < L.K; ++s) {
-    const int e = ws.ids[static_cast<size_t>(t) * L.K + s];
-    const int tiles = e >= 0 ? (counts[s] + kDownTileRows - 1) / kDownTileRows : 0;
-    if (tile >= tile_starts[s] && tile < tile_starts[s] + tiles) {
-      slot = s;
-      first = (tile - tile_starts[s]) * kDownTileRows;
-    }
-  }
-  if (slot < 0) return;
-  const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
-  const int rows = min(kDownTileRows, counts[slot] - first);
-  const int32_t* list =
-      ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[static_cast<size_t>(t) * L.K + slot] + first;
-  const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
-  // Stage the tile's channels and activations, then stream the rows.
+  constexpr int LANES = 128 / GROUPS, COLS = LANES * 8;
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
+  __shared__ float red[GROUPS > 1 ? GROUPS : 1][GROUPS > 1 ? COLS : 1];
+  __shared__ int s_slot, s_first;
+  const int t = blockIdx.z, tile = blockIdx.y, tid = threadIdx.x;
+  if (padding && padding[t]) return;
+  const size_t token_pairs = static_cast<size_t>(t) * L.K;
+  if (tid == 0) s_slot = -1;
+  __syncthreads();
+  if (tid < L.K) {  // the slot whose tile range holds this tile, if any
+    const int e = ws.ids[token_pairs + tid];
+    const int tiles =
+        e >= 0 ? (ws.counts[token_pairs + tid] + kDownTileRows - 1) / kDownTileRows : 0;
+    const int begin = ws.tile_starts[token_pairs + tid];
+    if (tile >= begin && tile < begin + tiles) {
+      s_slot = tid;
+      s_first = (tile - begin) * kDownTileRows;
+    }
+  }
+  __syncthreads();
+  const int slot = s_slot, first = s_first;
+  if (slot < 0) return;
+  const int e = ws.ids[token_pairs + slot];
+  const int rows = min(kDownTileRows, ws.counts[token_pairs + slot] - first);
+  const int32_t* list =
+      ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first;
+  const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
   if (tid < rows) {
     const int cid = list[tid];
     tile_channel[tid] = cid - slot * L.I;
     tile_activation[tid] = __bfloat162float(act[cid]);
   }
   __syncthreads();
-  const int group = tid >> 4, col = (tid & 15) * 8 + blockIdx.x * 128;
-  const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + col;
+  const int group = tid / LANES, lane = tid - group * LANES;
+  const int col = blockIdx.x * COLS + lane * 8;
+  const bool inside = col < L.H;
+  const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + (inside ? col : 0);
   float acc[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
   constexpr int U = 8;  // rows in flight per thread
-  for (int r0 = group; r0 < rows; r0 += 8 * U) {
+  for (int r0 = group; r0 < rows; r0 += GROUPS * U) {
     uint4 w[U];
     float a[U];
-    if (r0 + 8 * (U - 1) < rows) {
 #pragma unroll
-      for (int k = 0; k < U; ++k) {
-        const int r = r0 + 8 * k;
-        w[k] = load_stream16(base + static_cast<size_t>(tile_channel[r]) * L.H);
-        a[k] = tile_activation[r];
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < U; ++k) {
-        const int r = r0 + 8 * k;
-        w[k] = make_uint4(0, 0, 0, 0);
-        a[k] = 0.0f;
-        if (r < rows) {
-          w[k] = load_stream16(base + static_cast<size_t>(tile_channel[r]) * L.H);
-          a[k] = tile_activation[r];
-        }
-      }
+    for (int k = 0; k < U; ++k) {
+      const int r = min(r0 + GROUPS * k, rows - 1);
+      a[k] = r0 + GROUPS * k < rows ? tile_activation[r] : 0.0f;
+      w[k] = load_stream16(base + static_cast<size_t>(tile_channel[r]) * L.H);
     }
 #pragma unroll
     for (int k = 0; k < U; ++k) {
@@ -1077,14 +1076,27 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
       acc[7] = fmaf(bf16_hi(w[k].w), a[k], acc[7]);
     }
   }
-  __shared__ float red[8][128];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) red[group][(tid & 15) * 8 + j] = acc[j];
+  float* parts = ws.down_parts + (static_cast<size_t>(t) * ws.down_tiles + tile) * L.H;
+  if (GROUPS == 1) {
+    if (inside) {
+      float4* out = reinterpret_cast<float4*>(parts + col);
+      out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    return;
+  }
+  float4* mine = reinterpret_cast<float4*>(&red[GROUPS > 1 ? group : 0][GROUPS > 1 ? lane * 8 : 0]);
+  mine[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  mine[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
   __syncthreads();
-  float s = 0.0f;
+  for (int c = tid; c < COLS; c += 128) {
+    if (blockIdx.x * COLS + c < L.H) {
+      float sum = 0.0f;
 #pragma unroll
-  for (int g = 0; g < 8; ++g) s += red[g][tid];
-  ws.down_parts[(static_cast<size_t>(t) * ws.down_tiles + tile) * L.H + blockIdx.x * 128 + tid] = s;
+      for (int g2 = 0; g2 < GROUPS; ++g2) sum += red[GROUPS > 1 ? g2 : 0][GROUPS > 1 ? c : 0];
+      parts[blockIdx.x * COLS + c] = sum;
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1221,46 +1233,72 @@ __global__ void k_zero_latent(Layer L, Workspace ws) {
 __global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uint8_t* padding,
                                                 __nv_bfloat16* out) {
   __shared__ float latent[256];
+  __shared__ int slot_end[32];       // one past the last down tile of every slot
+  __shared__ float slot_weight[32];
   const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
   if (padding && padding[t]) {
     out[static_cast<size_t>(t) * L.H + h] = __float2bfloat16_rn(0.0f);
     return;
   }
   const bool recover = L.R > 0 && L.owner && L.decoder;
-  if (recover) {
+  if (tid < L.K) {
+    const size_t pair = static_cast<size_t>(t) * L.K + tid;
+    const int tiles =
+        ws.ids[pair] >= 0 ? (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows : 0;
+    slot_end[tid] = ws.tile_starts[pair] + tiles;
+    slot_weight[tid] = ws.weights[pair];
+  }
+  if (recover)
     for (int r = tid; r < L.R; r += 128)
       latent[r] = bf16_round(ws.latent[static_cast<size_t>(t) * L.R + r]);
-    __syncthreads();
-  }
-  float routed = 0.0f;
-  for (int s = 0; s < L.K; ++s) {
-    const size_t pair = static_cast<size_t>(t) * L.K + s;
-    if (ws.ids[pair] < 0) continue;
-    const int tiles = (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows;
-    if (!tiles) continue;
-    const float* p = ws.down_parts +
-                     (static_cast<size_t>(t) * ws.down_tiles + ws.tile_starts[pair]) * L.H + h;
-    float sum = 0.0f;
-    for (int j = 0; j < tiles; ++j) sum += p[static_cast<size_t>(j) * L.H];
-    routed = fmaf(bf16_round(sum), ws.weights[pair], routed);
-  }
+  // The decoder row does not depend on the slot table: fetch it first.
   float correction = 0.0f;
-  if (recover) {
-    const uint4* row = reinterpret_cast<const uint4*>(L.decoder + static_cast<size_t>(h) * L.R);
-    float sum = 0.0f;
-    for (int i = 0; i < L.R / 8; ++i) {
-      const uint4 w = row[i];
-      const float* z = latent + i * 8;
-      sum = fmaf(bf16_lo(w.x), z[0], sum);
-      sum = fmaf(bf16_hi(w.x), z[1], sum);
-      sum = fmaf(bf16_lo(w.y), z[2], sum);
-      sum = fmaf(bf16_hi(w.y), z[3], sum);
-      sum = fmaf(bf16_lo(w.z), z[4], sum);
-      sum = fmaf(bf16_hi(w.z), z[5], sum);
-      sum = fmaf(bf16_lo(w.w), z[6], sum);
-      sum = fmaf(bf16_hi(w.w), z[7], sum);
+  uint4 row[4];
+  const uint4* decoder_row = reinterpret_cast<const uint4*>(L.decoder + static_cast<size_t>(h) * L.R);
+  __syncthreads();
+  const int used = slot_end[L.K - 1];  // tiles are laid out slot after slot
+  // Per-slot sums of the tile partials, eight tile loads in flight.
+  const float* parts = ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h;
+  float routed = 0.0f, sum = 0.0f;
+  int slot = 0;
+  for (int base = 0; base < used; base += 8) {
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = base + j < used ? parts[static_cast<size_t>(base + j) * L.H] : 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int tile = base + j;
+      if (tile < used) {
+        while (tile >= slot_end[slot]) {  // close the finished slots
+          routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+          sum = 0.0f;
+          ++slot;
+        }
+        sum += v[j];
+      }
     }
-    correction = bf16_round(sum);
+  }
+  if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+  if (recover) {
+    float dot = 0.0f;
+    for (int i0 = 0; i0 < L.R / 8; i0 += 4) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) row[i] = i0 + i < L.R / 8 ? decoder_row[i0 + i] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (i0 + i >= L.R / 8) break;
+        const float* z = latent + (i0 + i) * 8;
+        dot = fmaf(bf16_lo(row[i].x), z[0], dot);
+        dot = fmaf(bf16_hi(row[i].x), z[1], dot);
+        dot = fmaf(bf16_lo(row[i].y), z[2], dot);
+        dot = fmaf(bf16_hi(row[i].y), z[3], dot);
+        dot = fmaf(bf16_lo(row[i].z), z[4], dot);
+        dot = fmaf(bf16_hi(row[i].z), z[5], dot);
+        dot = fmaf(bf16_lo(row[i].w), z[6], dot);
+        dot = fmaf(bf16_hi(row[i].w), z[7], dot);
+      }
+    }
+    correction = bf16_round(dot);
   }
   out[static_cast<size_t>(t) * L.H + h] = __float2bfloat16_rn(routed + correction);
 }
@@ -1403,7 +1441,7 @@ static int run_exact(const Bound& b, const cfm_call* call) {
 }
 
 static int run_down(const Bound& b) {
-  k_down<<<dim3(b.L.H / 128, b.ws.down_tiles, b.T), 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+  k_down<8><<<dim3(b.L.H / 128, b.ws.down_tiles, b.T), 128, 0, b.stream>>>(b.L, b.ws, b.padding);
   return launched();
 }
 
