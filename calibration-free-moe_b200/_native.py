@@ -28,9 +28,9 @@ NVCC_FLAGS = [
 # Entry points include/cfm_b200.h declares; `load()` checks each one resolves.
 STAGES = (
     "cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_score", "cfm_select", "cfm_exact",
-    "cfm_down", "cfm_encode", "cfm_output", "cfm_reader_forward",
+    "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_reader_forward",
 )
-SYMBOLS = ("cfm_abi_version", "cfm_error_string", "cfm_workspace_layout_for") + STAGES
+SYMBOLS = ("cfm_abi_version", "cfm_error_string", "cfm_workspace_layout_for", "cfm_finish") + STAGES
 
 
 class Layer(ctypes.Structure):
@@ -163,6 +163,11 @@ def load() -> ctypes.CDLL:
             ctypes.POINTER(Layer), ctypes.c_void_p, ctypes.c_int32, ctypes.POINTER(Call),
             ctypes.c_void_p,
         ]
+    library.cfm_finish.restype = ctypes.c_int
+    library.cfm_finish.argtypes = [
+        ctypes.POINTER(Layer), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_void_p,
+    ]
     _library = library
     return library
 

@@ -1303,6 +1303,74 @@ __global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uin
   out[static_cast<size_t>(t) * L.H + h] = __float2bfloat16_rn(routed + correction);
 }
 
+// Expert parallelism splits the output stage in two.  k_partial_output runs on
+// the rank that owns experts: the router-weighted FP32 sum of its local slots'
+// BF16-rounded expert sums, no decoder term.  k_finish runs on the token's home
+// rank after the partial sums and latents of all ranks have been added: decoder
+// term and BF16 store.  grid (H / 128, T), 128 threads each.
+__global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
+                                                        const uint8_t* padding, float* routed_out) {
+  __shared__ int slot_end[32];
+  __shared__ float slot_weight[32];
+  const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
+  if (padding && padding[t]) {
+    routed_out[static_cast<size_t>(t) * L.H + h] = 0.0f;
+    return;
+  }
+  if (tid < L.K) {
+    const size_t pair = static_cast<size_t>(t) * L.K + tid;
+    const int tiles =
+        ws.ids[pair] >= 0 ? (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows : 0;
+    slot_end[tid] = ws.tile_starts[pair] + tiles;
+    slot_weight[tid] = ws.weights[pair];
+  }
+  __syncthreads();
+  const int used = slot_end[L.K - 1];
+  const float* parts = ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h;
+  float routed = 0.0f, sum = 0.0f;
+  int slot = 0;
+  for (int tile = 0; tile < used; ++tile) {
+    while (tile >= slot_end[slot]) {
+      routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+      sum = 0.0f;
+      ++slot;
+    }
+    sum += parts[static_cast<size_t>(tile) * L.H];
+  }
+  if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+  routed_out[static_cast<size_t>(t) * L.H + h] = routed;
+}
+
+__global__ void __launch_bounds__(128) k_finish(Layer L, const float* routed, const float* latent_in,
+                                                __nv_bfloat16* out) {
+  __shared__ float latent[256];
+  const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
+  const bool recover = L.R > 0 && L.decoder && latent_in;
+  float correction = 0.0f;
+  if (recover) {
+    for (int r = tid; r < L.R; r += 128)
+      latent[r] = bf16_round(latent_in[static_cast<size_t>(t) * L.R + r]);
+    __syncthreads();
+    const uint4* row = reinterpret_cast<const uint4*>(L.decoder + static_cast<size_t>(h) * L.R);
+    float dot = 0.0f;
+    for (int i = 0; i < L.R / 8; ++i) {
+      const uint4 w = row[i];
+      const float* z = latent + i * 8;
+      dot = fmaf(bf16_lo(w.x), z[0], dot);
+      dot = fmaf(bf16_hi(w.x), z[1], dot);
+      dot = fmaf(bf16_lo(w.y), z[2], dot);
+      dot = fmaf(bf16_hi(w.y), z[3], dot);
+      dot = fmaf(bf16_lo(w.z), z[4], dot);
+      dot = fmaf(bf16_hi(w.z), z[5], dot);
+      dot = fmaf(bf16_lo(w.w), z[6], dot);
+      dot = fmaf(bf16_hi(w.w), z[7], dot);
+    }
+    correction = bf16_round(dot);
+  }
+  out[static_cast<size_t>(t) * L.H + h] =
+      __float2bfloat16_rn(routed[static_cast<size_t>(t) * L.H + h] + correction);
+}
+
 // ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
@@ -1541,6 +1609,30 @@ CFM_STAGE(cfm_exact, return run_exact(b, call);)
 CFM_STAGE(cfm_down, return run_down(b);)
 CFM_STAGE(cfm_encode, return run_encode(b);)
 CFM_STAGE(cfm_output, return run_output(b, call);)
+
+int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity,
+                       const cfm_call* call, void* stream) {
+  Bound b;
+  const int rc = bind_call(layer, workspace, capacity, call, stream, &b);
+  if (rc) return rc;
+  if (!call->out) return CFM_E_NULL;
+  k_partial_output<<<dim3(b.L.H / 128, b.T), 128, 0, b.stream>>>(
+      b.L, b.ws, b.padding, static_cast<float*>(call->out));
+  return launched();
+}
+
+int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* routed, const float* latent,
+               void* out, void* stream) {
+  if (!layer || !routed || !out) return CFM_E_NULL;
+  cfm_workspace_layout layout;
+  const int rc = make_layout(layer, 1, &layout);  // validates the dimensions
+  if (rc) return rc;
+  if (tokens < 1) return CFM_E_CAPACITY;
+  const Layer L = device_layer(layer);
+  k_finish<<<dim3(L.H / 128, tokens), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      L, routed, latent, static_cast<__nv_bfloat16*>(out));
+  return launched();
+}
 
 int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity,
                        const cfm_call* call, void* stream) {

@@ -198,6 +198,21 @@ int cfm_encode(const cfm_layer* layer, void* workspace, int32_t capacity,
 int cfm_output(const cfm_layer* layer, void* workspace, int32_t capacity,
                const cfm_call* call, void* stream);
 
+/* Expert parallelism, owner side: like cfm_output but call->out is f32 [T, H]
+ * and receives only the router-weighted sum of this rank's local slots (each
+ * expert sum rounded to BF16 first, as in _output); no decoder term.  The
+ * caller adds the ranks' partial sums and latents (`latent` of the workspace).
+ * Replaces: the per-rank part of _output (progressive.py:2019-2111). */
+int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity,
+                       const cfm_call* call, void* stream);
+
+/* Expert parallelism, home side: out = bf16(routed + bf16(U bf16(latent))) for
+ * `tokens` rows; routed f32 [T, H] and latent f32 [T, R] are the sums over the
+ * ranks (latent may be NULL without a recovery map).  Needs only hidden, rank
+ * and decoder of `layer`.  Replaces: the tail of _output (:2096-2111). */
+int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* routed, const float* latent,
+               void* out, void* stream);
+
 /* The whole layer on one stream: prepare (unless input_prepared), route,
  * screen, select, exact, down, encode, output.  Single-device readers only;
  * expert-parallel readers call the stages with their collectives between.

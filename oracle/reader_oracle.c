@@ -68,6 +68,10 @@ typedef struct oracle_result {
   int32_t* coordinates;   /* [T, B, KEEP] or NULL */
   float* latent;          /* [T, R] or NULL */
   float* output;          /* [T, H] output (BF16-rounded unless fp32 mode) */
+  float* routed;          /* [T, H] router-weighted sum of the local slots before the
+                             decoder term and the final rounding, or NULL */
+  const float* given_scores; /* [T, N] scores to select by instead of the computed ones
+                                (expert parallelism: sums over ranks), or NULL */
 } oracle_result;
 
 /* ---- number formats ---------------------------------------------------- */
@@ -352,6 +356,8 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
   if (out->partial) memcpy(out->partial + (int64_t)t * 2 * N, projection, sizeof(float) * 2 * N);
   if (out->scores) memcpy(out->scores + (int64_t)t * N, score, sizeof(float) * N);
 
+  if (out->given_scores) memcpy(score, out->given_scores + (int64_t)t * N, sizeof(float) * N);
+
   /* select: F best, ties to the lower candidate index */
   int32_t* kept = (int32_t*)malloc(sizeof(int32_t) * F);
   if (screened) {
@@ -420,6 +426,8 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
   }
   if (out->latent)
     for (int r = 0; r < R; ++r) out->latent[(int64_t)t * R + r] = (float)latent[r];
+  if (out->routed)
+    for (int h = 0; h < H; ++h) out->routed[(int64_t)t * H + h] = (float)routed[h];
   for (int h = 0; h < H; ++h) {
     double recovery = 0.0;
     if (R > 0 && L->decoder && L->recovery_owner) {
@@ -467,6 +475,9 @@ static void* worker(void* arg) {
     const oracle_result* out = j->out;
     if (j->padding && j->padding[t]) {
       memset(out->output + (int64_t)t * H, 0, sizeof(float) * H);
+      if (out->routed) memset(out->routed + (int64_t)t * H, 0, sizeof(float) * H);
+      if (out->latent && j->L->rank)
+        memset(out->latent + (int64_t)t * j->L->rank, 0, sizeof(float) * j->L->rank);
       if (out->scores) memset(out->scores + (int64_t)t * N, 0, sizeof(float) * N);
       if (out->partial) memset(out->partial + (int64_t)t * 2 * N, 0, sizeof(float) * 2 * N);
       if (out->selected) memset(out->selected + (int64_t)t * N, 0, (size_t)N);

@@ -58,6 +58,8 @@ class _Result(ctypes.Structure):
             "coordinates",
             "latent",
             "output",
+            "routed",
+            "given_scores",
         )
     ]
 
@@ -124,6 +126,7 @@ def forward(
     activation: str = "silu",
     fp32: bool = False,
     threads: int | None = None,
+    given_scores: Tensor | None = None,
 ) -> dict[str, Tensor]:
     """Run the oracle on T tokens.
 
@@ -132,7 +135,10 @@ def forward(
     sketch from `build_sketch`; encoder `[E, R, I]`, decoder `[H, R]` BF16 or
     None.  Returns projections, scores, selection, the per-token candidate list,
     the latent and the output (`[T, H]` FP32 holding BF16-rounded values, or the
-    unrounded FP32 evaluation with `fp32=True`).
+    unrounded FP32 evaluation with `fp32=True`).  `given_scores` `[T, N]` replaces
+    the computed scores for the selection (expert parallelism: the sum over
+    ranks); `routed` in the result is the FP32 router-weighted sum of the local
+    slots before the decoder term.
     """
     lib = load()
     h, i, k = plan.hidden_size, plan.expert_width, plan.top_k
@@ -179,8 +185,13 @@ def forward(
         "coordinates": torch.zeros(tokens, blocks, keep, dtype=torch.int32),
         "latent": torch.zeros(tokens, max(rank, 1)),
         "output": torch.zeros(tokens, h),
+        "routed": torch.zeros(tokens, h),
     }
-    result = _Result(*(out[name].data_ptr() for name, _ in _Result._fields_))
+    given = _cpu(given_scores, torch.float32) if given_scores is not None else None
+    result = _Result(
+        *(out[name].data_ptr() for name, _ in _Result._fields_[:-1]),
+        given.data_ptr() if given is not None else None,
+    )
     if threads is None:
         threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     code = lib.oracle_forward(

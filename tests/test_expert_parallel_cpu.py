@@ -1,0 +1,121 @@
+"""Expert-parallel orchestration on CPU: two gloo ranks, the oracle as the compute engine.
+
+Checks the host logic of `cfm_b200.reader.expert_parallel` (expert placement,
+dispatch, score exchange, combine) without a GPU: every rank holds half of the
+experts and half of the tokens; results must equal the single-process oracle on
+the whole layer (selections exactly, outputs to FP32 re-association).
+"""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from helpers import prepared, run_oracle
+
+
+def _free_port() -> int:
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return int(sock.getsockname()[1])
+
+
+class OracleEngine:
+    """CPU stand-in for `CudaEngine`, built on the oracle (test infrastructure)."""
+
+    def __init__(self, oracle, item, rank, world):
+        from cfm_b200.reader.expert_parallel import linear_expert_map
+
+        case = item["case"]
+        experts = case.gate_up.shape[0]
+        local = experts // world
+        span = slice(rank * local, (rank + 1) * local)
+        self.oracle, self.case = oracle, case
+        self.fixed = dict(
+            plan=case.plan, gate_up=case.gate_up[span], down=item["down"][span],
+            codes=item["codes"][span], statistics=item["statistics"][span], signs=item["signs"],
+            encoder=case.encoder[span] if case.encoder is not None else None,
+            decoder=case.decoder, activation=case.activation,
+            expert_map=linear_expert_map(experts, world, rank), threads=2,
+        )
+        self.selected = None
+
+    def screen(self, hidden, ids, weights, padding):
+        self.inputs = dict(hidden=hidden, ids=ids, weights=weights, padding=padding)
+        return self.oracle.forward(**self.fixed, **self.inputs)["scores"].clone()
+
+    def local(self, scores):
+        out = self.oracle.forward(**self.fixed, **self.inputs, given_scores=scores)
+        self.selected = out["selected"]
+        latent = out["latent"] if self.case.decoder is not None else None
+        return out["routed"], latent
+
+    def finish(self, routed, latent):
+        correction = 0.0
+        if latent is not None:
+            z = latent.bfloat16().float()
+            correction = (self.case.decoder.float() @ z.T).T.bfloat16().float()
+        return (routed + correction).bfloat16()
+
+
+def _worker(rank, world, port, name, results):
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    for entry in (str(root), str(root / "tests"), str(root / "tests" / "golden")):
+        if entry not in sys.path:
+            sys.path.insert(0, entry)
+    import cfm_b200  # noqa: F401
+    from cfm_b200.reader.expert_parallel import expert_parallel_forward
+    from oracle import reader_oracle
+
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        item = prepared(name)
+        case = item["case"]
+        tokens = case.hidden.shape[0] // world
+        rows = slice(rank * tokens, (rank + 1) * tokens)
+        padding = case.padding[rows] if case.padding is not None else None
+        engine = OracleEngine(reader_oracle, item, rank, world)
+        out = expert_parallel_forward(
+            engine, case.hidden[rows], case.ids[rows], case.weights[rows], padding
+        )
+        results[rank] = (out.float(), engine.selected)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name", ["tiny", "qwen35-e16-t4", "graph-routes"])
+def test_two_rank_expert_parallel_matches_single_process(oracle, name):
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), name, results), nprocs=world, join=True)
+    item = prepared(name)
+    case = item["case"]
+    want = run_oracle(oracle, item)
+    tokens = case.hidden.shape[0] // world
+    active = torch.ones(case.hidden.shape[0], dtype=torch.bool)
+    if case.padding is not None:
+        active = ~case.padding
+    for rank in range(world):
+        out, selected = results[rank]
+        rows = slice(rank * tokens, (rank + 1) * tokens)
+        # Every rank kept the same channels for every token, equal to the single-process result.
+        assert torch.equal(selected[active], want["selected"][active])
+        torch.testing.assert_close(out[active[rows]], want["output"][rows][active[rows]],
+                                   rtol=0.016, atol=2e-3)
+        assert not out[~active[rows]].any()
+
+
+def test_linear_expert_map():
+    from cfm_b200.reader.expert_parallel import linear_expert_map
+
+    assert linear_expert_map(8, 4, 1).tolist() == [-1, -1, 0, 1, -1, -1, -1, -1]
+    with pytest.raises(ValueError):
+        linear_expert_map(10, 4, 0)

@@ -1,0 +1,135 @@
+"""Expert parallelism on two GPUs over NCCL: the sharded reader against the single-GPU reader.
+
+Needs two devices; skipped otherwise.  Ranks are child processes, one per GPU.
+"""
+
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return int(sock.getsockname()[1])
+
+
+def _worker(rank, world, port, name, results):
+    import os
+    import sys
+    from pathlib import Path
+
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    root = Path(__file__).resolve().parents[1]
+    for entry in (str(root), str(root / "tests"), str(root / "tests" / "golden")):
+        if entry not in sys.path:
+            sys.path.insert(0, entry)
+    import cfm_b200  # noqa: F401
+    from cfm_b200.reader.expert_parallel import ExpertParallelReader, linear_expert_map
+    from cfm_b200.reader.progressive import ProgressiveReader
+    from helpers import prepared
+
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank,
+                            world_size=world, device_id=device)
+    try:
+        item = prepared(name)
+        case = item["case"]
+        experts = case.gate_up.shape[0]
+        local = experts // world
+        span = slice(rank * local, (rank + 1) * local)
+        tokens = case.hidden.shape[0] // world
+        rows = slice(rank * tokens, (rank + 1) * tokens)
+
+        def channel_major(down):
+            return down.transpose(1, 2).contiguous().to(device).transpose(1, 2)
+
+        def statistics(part):
+            return part.permute(0, 2, 3, 1).contiguous().to(device).permute(0, 3, 1, 2)
+
+        sharded = ExpertParallelReader(
+            case.gate_up[span].to(device), channel_major(item["down"][span]),
+            case.encoder[span].to(device) if case.encoder is not None else None,
+            case.decoder.to(device) if case.decoder is not None else None,
+            case.plan, tokens, global_experts=experts,
+            sketch=(item["codes"][span].to(device), statistics(item["statistics"][span])),
+            activation=case.activation, selection_score="point",
+        )
+        padding = case.padding[rows].to(device) if case.padding is not None else None
+        out = sharded(case.hidden[rows].to(device), case.ids[rows].to(device),
+                      case.weights[rows].to(device), padding)
+        torch.cuda.synchronize()
+        total = world * tokens
+        kept = sharded.reader.candidate_ids[-1][:total].cpu()
+        scores = sharded.reader.scores[0][:total].cpu()
+
+        # Reference-compatible mode: replicated tokens, all-reduce inside the reader.
+        replicated = ProgressiveReader(
+            case.gate_up[span].to(device), channel_major(item["down"][span]),
+            case.encoder[span].to(device) if case.encoder is not None else None,
+            case.decoder.to(device) if case.decoder is not None else None,
+            case.plan, case.hidden.shape[0],
+            expert_map=linear_expert_map(experts, world, rank),
+            sketch=(item["codes"][span].to(device), statistics(item["statistics"][span])),
+            activation=case.activation, selection_score="point",
+        )
+        all_padding = case.padding.to(device) if case.padding is not None else None
+        partial = replicated(case.hidden.to(device), case.ids.to(device),
+                             case.weights.to(device), all_padding).float()
+        dist.all_reduce(partial)
+        torch.cuda.synchronize()
+        compat_kept = replicated.candidate_ids[-1][: case.hidden.shape[0]].cpu()
+
+        expected = None
+        if rank == 0:
+            full = ProgressiveReader(
+                case.gate_up.to(device), channel_major(item["down"]),
+                case.encoder.to(device) if case.encoder is not None else None,
+                case.decoder.to(device) if case.decoder is not None else None,
+                case.plan, case.hidden.shape[0],
+                sketch=(item["codes"].to(device), statistics(item["statistics"])),
+                activation=case.activation, selection_score="point",
+            )
+            reference = full(case.hidden.to(device), case.ids.to(device),
+                             case.weights.to(device), all_padding)
+            torch.cuda.synchronize()
+            expected = (reference.float().cpu(), full.candidate_ids[-1][:total].cpu(),
+                        full.scores[0][:total].cpu())
+        results[rank] = (out.float().cpu(), kept, scores, partial.cpu(), compat_kept, expected)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("name", ["qwen35-e16-t4", "qwen3-e16-t8", "graph-routes"])
+def test_sharded_reader_matches_single_gpu(name):
+    from helpers import prepared
+
+    world = 2
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(world, _free_port(), name, results), nprocs=world, join=True)
+    case = prepared(name)["case"]
+    reference, kept, scores = results[0][5]
+    tokens = case.hidden.shape[0] // world
+    active = torch.ones(case.hidden.shape[0], dtype=torch.bool)
+    if case.padding is not None:
+        active = ~case.padding
+    envelope = 2 * torch.finfo(torch.bfloat16).eps * reference.abs().max().item()
+    for rank in range(world):
+        out, rank_kept, rank_scores, compat, compat_kept, _ = results[rank]
+        rows = slice(rank * tokens, (rank + 1) * tokens)
+        # Summed scores and kept channels equal the single-GPU reader's, bit for bit.
+        assert torch.equal(rank_scores[active], scores[active])
+        assert torch.equal(rank_kept[active], kept[active])
+        assert torch.equal(compat_kept[active], kept[active])
+        torch.testing.assert_close(out[active[rows]], reference[rows][active[rows]],
+                                   rtol=0, atol=envelope)
+        torch.testing.assert_close(compat[active], reference[active], rtol=0, atol=2 * envelope)
+        assert not out[~active[rows]].any()
