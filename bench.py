@@ -55,17 +55,23 @@ def measured_peaks() -> tuple[float, str]:
 # ---------------------------------------------------------------------------
 # workload
 # ---------------------------------------------------------------------------
-def device_layer(shape: synthetic.LayerShape, seed: int, device: torch.device):
-    """Random BF16 weights of one layer, drawn on the device."""
-    g = torch.Generator(device=device).manual_seed(seed)
-    e, h, i, r = shape.experts, shape.hidden, shape.width, shape.rank
+def device_layer(shape: synthetic.LayerShape, seed: int, device: torch.device,
+                 world: int = 1, rank: int = 0):
+    """Random BF16 weights of one layer, drawn on the device.
+
+    Under expert parallelism a rank draws only its E / world experts (own seed);
+    router and decoder are replicated (common seed).
+    """
+    g = torch.Generator(device=device).manual_seed(seed * 64 + rank + 1)
+    e, h, i, r = shape.experts // world, shape.hidden, shape.width, shape.rank
     gate_up = torch.empty(e, 2 * i, h, device=device, dtype=torch.bfloat16)
     down = torch.empty(e, i, h, device=device, dtype=torch.bfloat16)  # physical channel-major
     for expert in range(e):  # one expert at a time keeps the FP32 temporaries small
         gate_up[expert] = (torch.randn(2 * i, h, device=device, generator=g) * shape.sigma).bfloat16()
         down[expert] = (torch.randn(i, h, device=device, generator=g) * shape.sigma).bfloat16()
-    router = (torch.randn(e, h, device=device, generator=g) * shape.sigma).bfloat16()
-    decoder = torch.linalg.qr(torch.randn(h, r, device=device, generator=g)).Q.bfloat16()
+    common = torch.Generator(device=device).manual_seed(seed * 64)
+    router = (torch.randn(shape.experts, h, device=device, generator=common) * shape.sigma).bfloat16()
+    decoder = torch.linalg.qr(torch.randn(h, r, device=device, generator=common)).Q.bfloat16()
     encoder = torch.stack(
         [torch.linalg.qr(torch.randn(i, r, device=device, generator=g)).Q.T for _ in range(e)]
     ).bfloat16()
@@ -271,8 +277,17 @@ def workload_config(shape, plan, tokens, layers, gpus) -> dict:
         "screen_coordinates": plan.screen_coordinates, "selection_score": "point",
         "tokens_per_step": tokens, "layers_cycled": layers,
         "l2": f"steps cycle over {layers} layers with distinct weights, inputs and workspaces",
-        "parallelism": "single GPU" if gpus == 1 else f"{gpus} independent replicas",
+        "parallelism": "single GPU" if gpus == 1 else (
+            f"expert parallel over {gpus} GPUs: {shape.experts // gpus} experts per rank, "
+            f"{tokens} tokens per rank per step; all_gather dispatch, all_reduce of scores, "
+            "FP32 reduce_scatter combine (NCCL)"),
     }
+
+
+def trace(message: str) -> None:
+    """Progress marker on stderr when CFM_BENCH_TRACE is set (for diagnosing multi-rank runs)."""
+    if os.environ.get("CFM_BENCH_TRACE"):
+        print(f"[rank {os.environ.get('RANK', '0')}] {message}", file=sys.stderr, flush=True)
 
 
 def run_ours(args, shape, plan) -> None:
@@ -292,26 +307,40 @@ def run_ours(args, shape, plan) -> None:
 
         dist.init_process_group("nccl", device_id=device)
     tokens, layers = args.tokens, args.layers
-    readers, batches = [], []
+    readers, batches, sharded = [], [], []
     for index in range(layers):
-        gate_up, down, router, decoder, encoder, g = device_layer(shape, 1000 * rank + index, device)
-        readers.append(ProgressiveReader(
-            gate_up, down, encoder, decoder, plan, tokens,
-            selection_score="point", retain_reference_sketch=False,
-        ))
+        gate_up, down, router, decoder, encoder, g = device_layer(shape, index, device, world, rank)
+        if distributed:
+            from cfm_b200.reader.expert_parallel import ExpertParallelReader
+
+            sharded.append(ExpertParallelReader(
+                gate_up, down, encoder, decoder, plan, tokens, global_experts=shape.experts,
+                selection_score="point", retain_reference_sketch=False,
+            ))
+            readers.append(sharded[-1].reader)
+        else:
+            readers.append(ProgressiveReader(
+                gate_up, down, encoder, decoder, plan, tokens,
+                selection_score="point", retain_reference_sketch=False,
+            ))
         batches.append(device_batch(shape, router, tokens, g, device))
         del router
     outs = [torch.empty_like(b[0]) for b in batches]
     stream = torch.cuda.Stream(device)
+    trace("layers built")
 
     def step(index: int) -> None:
         hidden, ids, weights = batches[index]
-        readers[index](hidden, ids, weights, None, outs[index])
+        if distributed:
+            outs[index].copy_(sharded[index](hidden, ids, weights))
+        else:
+            readers[index](hidden, ids, weights, None, outs[index])
 
     with torch.cuda.stream(stream):
         for index in range(layers):
             step(index)
         stream.synchronize()
+        trace("eager steps done")
         graphs = []
         for index in range(layers):
             graph = torch.cuda.CUDAGraph()
@@ -324,6 +353,7 @@ def run_ours(args, shape, plan) -> None:
                 dist.barrier()
             torch.cuda.synchronize()
 
+        trace("graphs captured")
         # ---- resident-input throughput ---------------------------------
         for i in range(args.warmup):
             graphs[i % layers].replay()
@@ -337,6 +367,7 @@ def run_ours(args, shape, plan) -> None:
         barrier()
         elapsed_ms = begin.elapsed_time(end)
         clocks = sampler.stop() if sampler else None
+        trace("timed region done")
 
         # ---- end to end: host buffers, copies inside the timed region ---
         host_in = [tuple(t.cpu().pin_memory() for t in b) for b in batches]
@@ -359,6 +390,7 @@ def run_ours(args, shape, plan) -> None:
         end.record(stream)
         barrier()
         e2e_ms = max(begin.elapsed_time(end), 1e3 * (time.perf_counter() - start))
+        trace("end-to-end region done")
 
         # ---- per-stage device times (CUDA events on the launching stream) --
         # Every layer's workspace holds the state of its own last call, so one
@@ -367,7 +399,7 @@ def run_ours(args, shape, plan) -> None:
         # data that rotates through the layers like the steps above.
         library = _native.load()
         stage_ms = {}
-        calls = [
+        calls = [] if distributed else [
             readers[i]._call_struct(tokens, *batches[i], None, outs[i], False)
             for i in range(layers)
         ]
@@ -381,7 +413,7 @@ def run_ours(args, shape, plan) -> None:
                     ctypes.c_void_p(stream.cuda_stream)), name)
 
         repeats = max(3, min(20, args.steps // layers))
-        for name in STAGES:
+        for name in (() if distributed else STAGES):
             launch_stage(name)
             stream.synchronize()
             graph = torch.cuda.CUDAGraph()
@@ -394,22 +426,30 @@ def run_ours(args, shape, plan) -> None:
             end.record(stream)
             stream.synchronize()
             stage_ms[name] = begin.elapsed_time(end) / (repeats * layers)
-        bytes_by_kernel = algorithmic_bytes(readers[0], tokens)
+        bytes_by_kernel = algorithmic_bytes(readers[0], tokens * world)
         report = readers[0].report()
 
     times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
+    job_bytes = torch.tensor([bytes_by_kernel["total"]], device=device, dtype=torch.float64)
     if distributed:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dist.all_reduce(job_bytes)  # every rank reads its own experts' bytes
     elapsed_ms, e2e_ms = times.tolist()
+    bytes_by_kernel["total"] = float(job_bytes.item())
     if rank == 0:
         peak, peak_kind = measured_peaks()
         total_tokens = tokens * args.steps * world
-        dominant = max(stage_ms, key=stage_ms.get)
-        kernel = KERNEL_OF_STAGE[dominant]
-        kernel_bytes = bytes_by_kernel.get(kernel, 0.0)
-        achieved = kernel_bytes / (stage_ms[dominant] * 1e-3) / 1e9
         step_ms = elapsed_ms / args.steps
         layer_gbs = bytes_by_kernel["total"] / (step_ms * 1e-3) / 1e9
+        if stage_ms:
+            dominant = max(stage_ms, key=stage_ms.get)
+            kernel = KERNEL_OF_STAGE[dominant]
+            kernel_bytes = bytes_by_kernel.get(kernel, 0.0)
+            kernel_ms = stage_ms[dominant]
+        else:  # expert parallel: the whole layer, all ranks, against N times the peak
+            kernel, kernel_bytes, kernel_ms = "whole layer, all ranks", bytes_by_kernel["total"], step_ms
+        achieved = kernel_bytes / (kernel_ms * 1e-3) / 1e9
+        peak = peak * (1 if stage_ms else world)
         h2d = sum(t.numel() * t.element_size() for t in host_in[0])
         d2h = host_out[0].numel() * host_out[0].element_size()
         line = {
@@ -421,17 +461,18 @@ def run_ours(args, shape, plan) -> None:
             "clocks": clocks,
             "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": len(STAGES) * args.steps,
+            "gpu_launches": (len(STAGES) + (3 if distributed else 1)) * args.steps,
             "roofline": {
                 "bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": None,
                 "algorithmic_bytes_per_launch": kernel_bytes,
-                "ms_per_launch": stage_ms[dominant], "peak_source": peak_kind,
+                "ms_per_launch": kernel_ms, "peak_source": peak_kind,
             },
             "layer_roofline": {
                 "algorithmic_bytes_per_step": bytes_by_kernel["total"], "achieved": layer_gbs,
-                "peak": peak, "unit": "GB/s", "frac": layer_gbs / peak,
-                "frac_of_nominal_8000": layer_gbs / 8000.0,
+                "peak": peak if not stage_ms else peak * world, "unit": "GB/s",
+                "frac": layer_gbs / (peak if not stage_ms else peak * world),
+                "frac_of_nominal_8000": layer_gbs / (8000.0 * world),
             },
             "stage_ms": {KERNEL_OF_STAGE[k]: round(v, 5) for k, v in stage_ms.items()},
             "read_cost_bytes_per_token": report["charged_bytes"]
@@ -442,8 +483,16 @@ def run_ours(args, shape, plan) -> None:
             line["cpu_baseline"] = cpu_oracle_rate(shape, plan, min(tokens, 64))
         print(json.dumps(line))
     if distributed:
+        # Tearing down a NCCL communicator while CUDA graphs that captured its
+        # collectives are alive blocks on this stack; release the graphs, meet at
+        # a barrier, and leave without the communicator teardown.
+        del graphs
+        torch.cuda.synchronize()
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main() -> None:

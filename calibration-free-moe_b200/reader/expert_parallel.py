@@ -71,7 +71,10 @@ class Engine(Protocol):
 
 def _all_gather_rows(tensor: Tensor, world: int, group) -> Tensor:
     out = tensor.new_empty((world * tensor.shape[0], *tensor.shape[1:]))
-    dist.all_gather(list(out.chunk(world)), tensor.contiguous(), group=group)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(out, tensor.contiguous(), group=group)
+    else:
+        dist.all_gather(list(out.chunk(world)), tensor.contiguous(), group=group)
     return out
 
 
