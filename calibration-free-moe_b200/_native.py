@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -73,7 +73,7 @@ class Call(ctypes.Structure):
         ("weights_are_bf16", ctypes.c_int32),
         ("input_prepared", ctypes.c_int32),
         ("scores_ready", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("row_offset", ctypes.c_int32),
         ("hidden", ctypes.c_void_p),
         ("ids", ctypes.c_void_p),
         ("weights", ctypes.c_void_p),
@@ -86,7 +86,7 @@ _LAYOUT_ARRAYS = (
     "ids", "weights", "norms", "planes", "coordinates", "quantized", "exponents", "parts",
     "counters", "partial", "scores", "selected", "completed", "candidate_ids", "counts",
     "starts", "tile_starts", "activations", "exact", "down_parts", "encoder_parts", "latent",
-    "status", "limbs", "group_offsets", "group_pairs",
+    "status", "limbs", "group_offsets", "group_pairs", "cuts",
 )
 
 
@@ -166,7 +166,6 @@ def load() -> ctypes.CDLL:
     library.cfm_finish.restype = ctypes.c_int
     library.cfm_finish.argtypes = [
         ctypes.POINTER(Layer), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
-        ctypes.c_void_p,
     ]
     _library = library
     return library

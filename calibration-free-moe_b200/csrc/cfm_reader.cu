@@ -55,6 +55,7 @@ struct Workspace {
   int8_t* limbs;
   int32_t* group_offsets;
   int32_t* group_pairs;
+  int32_t* cuts;
   int32_t parts_tokens;
   int32_t down_tiles;
   int32_t encoder_tiles;
@@ -126,6 +127,7 @@ static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layou
   o->limbs = take(C * B * 3 * kBlock);
   o->group_offsets = take(4 * (static_cast<int64_t>(l->experts > 0 ? l->experts : 1) + 1));
   o->group_pairs = take(4 * C * K);
+  o->cuts = take(4 * C * (K + 1));
   o->bytes = at;
   return 0;
 }
@@ -159,6 +161,7 @@ static Workspace bind(const cfm_workspace_layout& o, void* base, int32_t capacit
   w.limbs = reinterpret_cast<int8_t*>(p + o.limbs);
   w.group_offsets = reinterpret_cast<int32_t*>(p + o.group_offsets);
   w.group_pairs = reinterpret_cast<int32_t*>(p + o.group_pairs);
+  w.cuts = reinterpret_cast<int32_t*>(p + o.cuts);
   w.parts_tokens = o.parts_tokens;
   w.down_tiles = o.down_tiles;
   w.encoder_tiles = o.encoder_tiles;
@@ -708,19 +711,21 @@ __device__ __forceinline__ int64_t sector_run(int64_t bytes) { return (bytes + 3
 // grid (T), 1024 threads, dynamic shared memory: N keys.
 __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws,
                                                            const uint8_t* padding,
-                                                           int scores_ready) {
+                                                           int scores_ready, int row_offset) {
   extern __shared__ uint32_t keys[];
   __shared__ int hist[2048];
   __shared__ int warp_above[32], warp_ties[32];
   __shared__ int s_digit, s_remaining;
-  __shared__ int s_starts[33];
-  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  __shared__ int s_starts[33], s_tie_start[33], s_budget[32];
+  const int t = blockIdx.x + row_offset, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int N = L.N, F = L.F, K = L.K, I = L.I;
+  const bool cut_given = scores_ready == 2, cut_only = scores_ready == 3;
   int32_t* counts = ws.counts + static_cast<size_t>(t) * K;
   int32_t* starts = ws.starts + static_cast<size_t>(t) * K;
   int32_t* tile_starts = ws.tile_starts + static_cast<size_t>(t) * K;
   if (padding && padding[t]) {
     if (tid < K) counts[tid] = starts[tid] = tile_starts[tid] = 0;
+    if (tid <= K) ws.cuts[static_cast<size_t>(t) * (K + 1) + tid] = 0;
     return;
   }
   const bool screened = F < N;
@@ -751,7 +756,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     uint32_t prefix = 0, mask = 0;
     int remaining = F;
 #pragma unroll 1
-    for (int pass = 0; pass < 3; ++pass) {
+    for (int pass = 0; pass < (cut_given ? 0 : 3); ++pass) {
       const int shift = pass == 0 ? 21 : pass == 1 ? 10 : 0;
       const int bins = pass == 2 ? 1024 : 2048;
       for (int i = tid; i < bins; i += kSelectThreads) hist[i] = 0;
@@ -799,61 +804,95 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     take_ties = remaining;
   }
 
-  // Compaction in candidate order: thread owns a contiguous chunk.
+  // Compaction in candidate order: a thread owns a contiguous chunk.  Ties at
+  // the cut are kept in candidate order; that rule is applied slot by slot with a
+  // per-slot tie budget, so that a rank holding only some of a token's slots can
+  // repeat the selection from the cut and the budgets alone.
   const int chunk = (N + kSelectThreads - 1) / kSelectThreads;
   const int begin = min(N, tid * chunk), end = min(N, begin + chunk);
-  int above = 0, ties = 0;
-  if (screened) {
-    for (int i = begin; i < end; ++i) {
-      const uint32_t k = keys[i];
-      above += k > cut;
-      ties += k == cut;
-    }
-  } else {
-    above = end - begin;
-  }
-  int above_scan = above, ties_scan = ties;
+  const int32_t* route = ws.ids + static_cast<size_t>(t) * K;
+  int32_t* cuts = ws.cuts + static_cast<size_t>(t) * (K + 1);
+  if (cut_given) cut = static_cast<uint32_t>(cuts[0]);
+  auto block_exclusive = [&](int value, int* total) {
+    int scan = value;
 #pragma unroll
-  for (int w = 1; w < 32; w <<= 1) {
-    const int oa = __shfl_up_sync(kFull, above_scan, w);
-    const int ot = __shfl_up_sync(kFull, ties_scan, w);
-    if (lane >= w) {
-      above_scan += oa;
-      ties_scan += ot;
+    for (int w = 1; w < 32; w <<= 1) {
+      const int o = __shfl_up_sync(kFull, scan, w);
+      if (lane >= w) scan += o;
     }
-  }
-  if (lane == 31) {
-    warp_above[warp] = above_scan;
-    warp_ties[warp] = ties_scan;
+    __syncthreads();  // previous use of warp_above is over
+    if (lane == 31) warp_above[warp] = scan;
+    __syncthreads();
+    int before = scan - value, sum = 0;
+    for (int w = 0; w < 32; ++w) {
+      if (w < warp) before += warp_above[w];
+      sum += warp_above[w];
+    }
+    *total = sum;
+    return before;
+  };
+  int ties = 0;
+  if (screened)
+    for (int i = begin; i < end; ++i) ties += keys[i] == cut;
+  int all_ties = 0;
+  const int ties_before = block_exclusive(ties, &all_ties);
+  {
+    int running = ties_before;
+    for (int i = begin; i < end; ++i) {
+      if (i % I == 0) s_tie_start[i / I] = running;
+      running += screened && keys[i] == cut;
+    }
+    if (tid == 0) s_tie_start[K] = all_ties;
   }
   __syncthreads();
-  int above_before = above_scan - above, ties_before = ties_scan - ties;
-  for (int w = 0; w < warp; ++w) {
-    above_before += warp_above[w];
-    ties_before += warp_ties[w];
+  if (tid < K) {
+    int budget;
+    if (cut_given) {
+      budget = cuts[1 + tid];
+    } else {
+      const int in_slot = s_tie_start[tid + 1] - s_tie_start[tid];
+      budget = max(0, min(in_slot, take_ties - s_tie_start[tid]));
+      cuts[1 + tid] = budget;
+      if (tid == 0) cuts[0] = static_cast<int32_t>(cut);
+    }
+    s_budget[tid] = budget;
   }
-  int position = above_before + min(ties_before, take_ties);
+  if (cut_only) return;  // the token's home rank only publishes the cut and the budgets
+  __syncthreads();
+  auto keeps = [&](int i, int running) {
+    const int slot = i / I;
+    if (cut_given && route[slot] < 0) return false;  // another rank's slot
+    if (!screened) return true;
+    const uint32_t k = keys[i];
+    return k > cut || (k == cut && running - s_tie_start[slot] < s_budget[slot]);
+  };
+  int kept = 0;
+  {
+    int running = ties_before;
+    for (int i = begin; i < end; ++i) {
+      kept += keeps(i, running);
+      running += screened && keys[i] == cut;
+    }
+  }
+  int total_kept = 0;
+  int position = block_exclusive(kept, &total_kept);
   uint8_t* selected = ws.selected + static_cast<size_t>(t) * N;
   uint8_t* completed = ws.completed + static_cast<size_t>(t) * N;
   int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * F;
-  const int32_t* route = ws.ids + static_cast<size_t>(t) * K;
-  for (int i = begin; i < end; ++i) {
-    bool keep = true;
-    if (screened) {
-      const uint32_t k = keys[i];
-      keep = k > cut;
-      if (k == cut) {
-        keep = ties_before < take_ties;
-        ++ties_before;
-      }
+  {
+    int running = ties_before;
+    for (int i = begin; i < end; ++i) {
+      const bool keep = keeps(i, running);
+      running += screened && keys[i] == cut;
+      const int slot = i / I;
+      if (i - slot * I == 0) s_starts[slot] = position;
+      selected[i] = keep;
+      completed[i] = keep && route[slot] >= 0;
+      if (keep) list[position++] = i;
     }
-    const int slot = i / I;
-    if (i - slot * I == 0) s_starts[slot] = position;
-    selected[i] = keep;
-    completed[i] = keep && route[slot] >= 0;
-    if (keep) list[position++] = i;
   }
-  if (tid == 0) s_starts[K] = F;
+  for (int i = total_kept + tid; i < F; i += kSelectThreads) list[i] = -1;
+  if (tid == 0) s_starts[K] = total_kept;
   __syncthreads();
   if (warp == 0) {
     const bool live = lane < K;
@@ -932,6 +971,17 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
   extern __shared__ uint4 xs[];  // H bf16 values of the token
   const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (padding && padding[t]) return;
+  if (L.expert_map) {
+    // Expert parallel: leave before staging the input when none of this CTA's
+    // candidates belongs to a local expert (most do not).
+    const int probe = blockIdx.x * kExactWarps + warp;
+    bool mine = false;
+    if (probe < L.F) {
+      const int cid = ws.candidate_ids[static_cast<size_t>(t) * L.F + probe];
+      mine = cid >= 0 && ws.ids[static_cast<size_t>(t) * L.K + cid / L.I] >= 0;
+    }
+    if (!__syncthreads_or(mine)) return;
+  }
   const int chunks = L.H / 8;
   const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
   for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
@@ -1309,12 +1359,17 @@ __global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uin
 // rank after the partial sums and latents of all ranks have been added: decoder
 // term and BF16 store.  grid (H / 128, T), 128 threads each.
 __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
-                                                        const uint8_t* padding, float* routed_out) {
+                                                        const uint8_t* padding, float* combined) {
   __shared__ int slot_end[32];
   __shared__ float slot_weight[32];
   const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
-  if (padding && padding[t]) {
-    routed_out[static_cast<size_t>(t) * L.H + h] = 0.0f;
+  float* routed_out = combined + static_cast<size_t>(t) * (L.H + L.R);
+  const bool padded = padding && padding[t];
+  if (blockIdx.x == 0)  // this rank's share of the latent rides behind the H outputs
+    for (int r = tid; r < L.R; r += 128)
+      routed_out[L.H + r] = padded ? 0.0f : ws.latent[static_cast<size_t>(t) * L.R + r];
+  if (padded) {
+    routed_out[h] = 0.0f;
     return;
   }
   if (tid < L.K) {
@@ -1338,18 +1393,19 @@ __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
     sum += parts[static_cast<size_t>(tile) * L.H];
   }
   if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
-  routed_out[static_cast<size_t>(t) * L.H + h] = routed;
+  routed_out[h] = routed;
 }
 
-__global__ void __launch_bounds__(128) k_finish(Layer L, const float* routed, const float* latent_in,
+__global__ void __launch_bounds__(128) k_finish(Layer L, const float* combined,
                                                 __nv_bfloat16* out) {
   __shared__ float latent[256];
   const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
-  const bool recover = L.R > 0 && L.decoder && latent_in;
+  const float* row_in = combined + static_cast<size_t>(blockIdx.y) * (L.H + L.R);
+  const bool recover = L.R > 0 && L.decoder;
   float correction = 0.0f;
   if (recover) {
     for (int r = tid; r < L.R; r += 128)
-      latent[r] = bf16_round(latent_in[static_cast<size_t>(t) * L.R + r]);
+      latent[r] = bf16_round(row_in[L.H + r]);
     __syncthreads();
     const uint4* row = reinterpret_cast<const uint4*>(L.decoder + static_cast<size_t>(h) * L.R);
     float dot = 0.0f;
@@ -1368,7 +1424,7 @@ __global__ void __launch_bounds__(128) k_finish(Layer L, const float* routed, co
     correction = bf16_round(dot);
   }
   out[static_cast<size_t>(t) * L.H + h] =
-      __float2bfloat16_rn(routed[static_cast<size_t>(t) * L.H + h] + correction);
+      __float2bfloat16_rn(row_in[h] + correction);
 }
 
 // ---------------------------------------------------------------------------
@@ -1379,6 +1435,7 @@ struct Bound {
   Workspace ws;
   cudaStream_t stream;
   int T;
+  int row_offset;  // first workspace row of the call (cfm_select only)
   const uint8_t* padding;
 };
 
@@ -1388,7 +1445,8 @@ static int bind_call(const cfm_layer* layer, void* workspace, int32_t capacity,
   cfm_workspace_layout layout;
   const int rc = make_layout(layer, capacity, &layout);
   if (rc) return rc;
-  if (call->tokens < 1 || call->tokens > capacity) return CFM_E_CAPACITY;
+  if (call->tokens < 1 || call->row_offset < 0 || call->tokens + call->row_offset > capacity)
+    return CFM_E_CAPACITY;
   if (layer->experts < 1 || !layer->gate_up || !layer->down) return CFM_E_NULL;
   if (layer->activation != CFM_ACT_SILU && layer->activation != CFM_ACT_GELU_TANH)
     return CFM_E_UNSUPPORTED;
@@ -1401,6 +1459,7 @@ static int bind_call(const cfm_layer* layer, void* workspace, int32_t capacity,
   b->ws = bind(layout, workspace, capacity);
   b->stream = static_cast<cudaStream_t>(stream);
   b->T = call->tokens;
+  b->row_offset = call->row_offset;
   b->padding = call->padding;
   return 0;
 }
@@ -1485,7 +1544,8 @@ static int run_select(const Bound& b, int scores_ready) {
         k_select, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);
   }
-  k_select<<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready);
+  k_select<<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready,
+                                                    b.row_offset);
   return launched();
 }
 
@@ -1621,16 +1681,16 @@ int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity
   return launched();
 }
 
-int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* routed, const float* latent,
-               void* out, void* stream) {
-  if (!layer || !routed || !out) return CFM_E_NULL;
+int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined, void* out,
+               void* stream) {
+  if (!layer || !combined || !out) return CFM_E_NULL;
   cfm_workspace_layout layout;
   const int rc = make_layout(layer, 1, &layout);  // validates the dimensions
   if (rc) return rc;
   if (tokens < 1) return CFM_E_CAPACITY;
   const Layer L = device_layer(layer);
   k_finish<<<dim3(L.H / 128, tokens), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      L, routed, latent, static_cast<__nv_bfloat16*>(out));
+      L, combined, static_cast<__nv_bfloat16*>(out));
   return launched();
 }
 
@@ -1750,6 +1810,7 @@ extern "C" int cfm_screen_static(const cfm_layer* layer, const cfm_static_screen
   b.ws = ws;
   b.stream = static_cast<cudaStream_t>(stream);
   b.T = io->tokens;
+  b.row_offset = 0;
   b.padding = io->padding;
   // The arrival counters must start at zero; the products need no clearing
   // (every entry that is read has been written by this call).

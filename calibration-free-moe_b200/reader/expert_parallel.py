@@ -9,23 +9,29 @@ outputs back.
 One layer call, on every rank:
 
 1. dispatch   every rank's tokens, router ids and weights reach the ranks that
-              own their experts (`all_gather`; with K = 8 experts over at most 8
-              ranks nearly every token has an expert on every rank, so the
-              dispatch of a static-shape decode step is the gather of all rows);
+              own their experts (`all_gather` of the hidden rows and of one packed
+              routing record per token; with K = 8 experts over at most 8 ranks
+              nearly every token has an expert on every rank, so the dispatch of
+              a static-shape decode step is the gather of all rows);
 2. screen     each rank scores the candidate channels of its local experts for
               all `P * T` tokens; slots of remote experts score zero;
-3. exchange   the per-token top-F is global over the token's K experts, so the
-              scores are summed across ranks (`all_reduce`) and every rank then
-              keeps the same channels (reference progressive.py:4245-4251);
-4. local      each rank computes its kept channels exactly, their down rows and
-              its share of the recovery latent;
-5. combine    the FP32 router-weighted partial outputs and partial latents go
-              back to the token's home rank (`reduce_scatter`), which adds the
-              decoder term and stores BF16.
+3. exchange   the per-token top-F is global over the token's K experts: the
+              score rows are summed onto each token's home rank
+              (`reduce_scatter`), the home rank finds the cut (the F-th largest
+              score and, per slot, how many candidates tied with it are kept)
+              and publishes 4 (K + 1) bytes per token (`all_gather`);
+4. local      each rank repeats the selection for its own slots from the cut,
+              computes those channels exactly, their down rows and its share of
+              the recovery latent;
+5. combine    one FP32 row per token (router-weighted partial output followed
+              by the partial latent) goes back to the token's home rank
+              (`reduce_scatter`), which adds the decoder term and stores BF16.
 
-Compared with the reference's expert-parallel mode (replicated tokens, caller
-all-reduces BF16 outputs: tests/test_expert_parallel_reader.py:128-130) tokens
-stay sharded and the output is reduced in FP32 before its single BF16 rounding.
+Compared with the reference's expert-parallel mode (replicated tokens, scores
+all-reduced, caller all-reduces BF16 outputs: progressive.py:4245-4251,
+tests/test_expert_parallel_reader.py:128-130) tokens stay sharded, the selection
+runs once per token instead of once per rank, and the output is reduced in FP32
+before its single BF16 rounding.  The kept channels are the same bit for bit.
 
 The collectives are plain `torch.distributed` calls on tensors, so the same
 orchestration runs over NCCL with the CUDA engine and over gloo with a CPU
@@ -60,13 +66,16 @@ class Engine(Protocol):
     """What the orchestration needs from one rank's compute back end."""
 
     def screen(self, hidden: Tensor, ids: Tensor, weights: Tensor, padding: Tensor | None) -> Tensor:
-        """Scores `[rows, N]` of the local experts' channels (zero elsewhere)."""
+        """Score buffer `[rows, N]`: the local experts' channels scored, zero elsewhere."""
 
-    def local(self, scores: Tensor) -> tuple[Tensor, Tensor | None]:
-        """Given the summed scores: FP32 partial outputs `[rows, H]` and latents `[rows, R]`."""
+    def find_cuts(self, first_row: int, rows: int) -> Tensor:
+        """Cut buffer `[all rows, 1 + K]` with rows `first_row ..` filled from the summed scores."""
 
-    def finish(self, routed: Tensor, latent: Tensor | None) -> Tensor:
-        """Home-rank output `[T, H]` BF16 from the summed partials."""
+    def local(self) -> Tensor:
+        """From the gathered cuts: FP32 rows `[all rows, H + R]` (partial output, partial latent)."""
+
+    def finish(self, combined: Tensor) -> Tensor:
+        """Home-rank output `[T, H]` BF16 from the summed rows."""
 
 
 def _all_gather_rows(tensor: Tensor, world: int, group) -> Tensor:
@@ -78,17 +87,25 @@ def _all_gather_rows(tensor: Tensor, world: int, group) -> Tensor:
     return out
 
 
-def _reduce_scatter_rows(tensor: Tensor, world: int, rank: int, group) -> Tensor:
-    """Sum `tensor` over ranks and return this rank's block of rows."""
-    rows = tensor.shape[0] // world
+def _all_gather_in_place(buffer: Tensor, world: int, rank: int, group) -> None:
+    """Fill `buffer` (rows of all ranks) from each rank's own block of rows."""
+    rows = buffer.shape[0] // world
+    mine = buffer[rank * rows : (rank + 1) * rows]
     if dist.get_backend(group) == "nccl":
-        out = tensor.new_empty((rows, *tensor.shape[1:]))
-        dist.reduce_scatter_tensor(out, tensor.contiguous(), group=group)
-        return out
-    # gloo has no reduce-scatter: reduce everything, keep the local block.
-    total = tensor.clone()
-    dist.all_reduce(total, group=group)
-    return total[rank * rows : (rank + 1) * rows].contiguous()
+        dist.all_gather_into_tensor(buffer, mine, group=group)
+    else:
+        dist.all_gather(list(buffer.chunk(world)), mine.clone(), group=group)
+
+
+def _reduce_scatter_in_place(buffer: Tensor, world: int, rank: int, group) -> Tensor:
+    """Sum `buffer` over ranks; this rank's block of rows receives its sum and is returned."""
+    rows = buffer.shape[0] // world
+    mine = buffer[rank * rows : (rank + 1) * rows]
+    if dist.get_backend(group) == "nccl":
+        dist.reduce_scatter_tensor(mine, buffer, group=group)
+    else:  # gloo has no reduce-scatter: reduce everything
+        dist.all_reduce(buffer, group=group)
+    return mine
 
 
 def expert_parallel_forward(
@@ -101,19 +118,24 @@ def expert_parallel_forward(
 ) -> Tensor:
     """One layer call under expert parallelism (see the module docstring)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
+    tokens, k = ids.shape
+    # One routing record per token: ids, weight bits, padding flag, as int32.
+    record = torch.empty((tokens, 2 * k + 1), device=ids.device, dtype=torch.int32)
+    record[:, :k] = ids
+    record[:, k : 2 * k] = weights.float().contiguous().view(torch.int32)
+    record[:, 2 * k] = padding.to(torch.int32) if padding is not None else 0
     all_hidden = _all_gather_rows(hidden, world, group)
-    all_ids = _all_gather_rows(ids, world, group)
-    all_weights = _all_gather_rows(weights, world, group)
-    all_padding = None
-    if padding is not None:
-        all_padding = _all_gather_rows(padding.to(torch.uint8), world, group).bool()
+    all_records = _all_gather_rows(record, world, group)
+    all_ids = all_records[:, :k].contiguous()
+    all_weights = all_records[:, k : 2 * k].contiguous().view(torch.float32)
+    all_padding = all_records[:, 2 * k].bool() if padding is not None else None
     scores = engine.screen(all_hidden, all_ids, all_weights, all_padding)
-    dist.all_reduce(scores, group=group)
-    routed, latent = engine.local(scores)
-    routed = _reduce_scatter_rows(routed, world, rank, group)
-    if latent is not None:
-        latent = _reduce_scatter_rows(latent, world, rank, group)
-    return engine.finish(routed, latent)
+    _reduce_scatter_in_place(scores, world, rank, group)
+    cuts = engine.find_cuts(rank * tokens, tokens)
+    _all_gather_in_place(cuts, world, rank, group)
+    combined = engine.local()
+    mine = _reduce_scatter_in_place(combined, world, rank, group)
+    return engine.finish(mine)
 
 
 class CudaEngine:
@@ -124,40 +146,68 @@ class CudaEngine:
         self._call: _native.Call | None = None
         self._rows = 0
         capacity, h = reader.max_tokens, reader.plan.hidden_size
-        self._routed = torch.empty(capacity, h, device=reader.native_gu.device, dtype=torch.float32)
+        device = reader.native_gu.device
+        self._combined = torch.empty(capacity, h + reader.rank, device=device, dtype=torch.float32)
+        # The recovery encoder runs beside the two gathers on its own stream.
+        self._side = torch.cuda.Stream(device, priority=-1)
+        self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
 
     def screen(self, hidden, ids, weights, padding):
         reader = self.reader
         rows = reader._validate_input(hidden, padding)
-        call = reader._call_struct(rows, hidden, ids, weights, padding, self._routed, False)
+        call = reader._call_struct(rows, hidden, ids, weights, padding, self._combined, False)
         self._keep = (hidden, ids, weights, padding)  # the call struct holds raw pointers
+        screened = reader.plan.completion_count < reader.plan.candidate_count
         with torch.cuda.device(reader.native_gu.device):
-            if reader.plan.completion_count < reader.plan.candidate_count:
+            if screened:
                 reader._stage("cfm_prepare_input", call)
             reader._stage("cfm_route", call)
-            if reader.plan.completion_count < reader.plan.candidate_count:
+            if screened:
                 reader._stage("cfm_screen", call)
                 reader._stage("cfm_score", call)
+            else:
+                reader.scores[0][:rows].zero_()
         self._call, self._rows = call, rows
         return reader.scores[0][:rows]
 
-    def local(self, scores):
-        reader, call = self.reader, self._call
-        call.scores_ready = 1
-        with torch.cuda.device(reader.native_gu.device):
-            for stage in ("cfm_select", "cfm_exact", "cfm_down", "cfm_encode", "cfm_partial_output"):
-                reader._stage(stage, call)
-        latent = reader.latent[: self._rows] if reader.rank else None
-        return self._routed[: self._rows], latent
-
-    def finish(self, routed, latent):
+    def find_cuts(self, first_row, rows):
         reader = self.reader
-        out = torch.empty(routed.shape, device=routed.device, dtype=torch.bfloat16)
-        stream = torch.cuda.current_stream(routed.device).cuda_stream
-        with torch.cuda.device(routed.device):
+        # Workspace rows (and the padding mask) are indexed by absolute row.
+        home = reader._call_struct(rows, *self._keep, self._combined, False)
+        home.scores_ready, home.row_offset = 3, first_row
+        with torch.cuda.device(reader.native_gu.device):
+            reader._stage("cfm_select", home)
+        return reader.workspace.cuts[: self._rows]
+
+    def local(self):
+        reader, call = self.reader, self._call
+        call.scores_ready = 2
+        device = reader.native_gu.device
+        with torch.cuda.device(device):
+            reader._stage("cfm_select", call)
+            main = torch.cuda.current_stream(device)
+            if reader.rank:
+                self._fork.record(main)
+                with torch.cuda.stream(self._side):
+                    self._side.wait_event(self._fork)
+                    reader._stage("cfm_encode", call)
+                    self._join.record(self._side)
+            reader._stage("cfm_exact", call)
+            reader._stage("cfm_down", call)
+            if reader.rank:
+                main.wait_event(self._join)
+            reader._stage("cfm_partial_output", call)
+        return self._combined[: self._rows]
+
+    def finish(self, combined):
+        reader = self.reader
+        rows = combined.shape[0]
+        out = torch.empty((rows, reader.plan.hidden_size), device=combined.device,
+                          dtype=torch.bfloat16)
+        stream = torch.cuda.current_stream(combined.device).cuda_stream
+        with torch.cuda.device(combined.device):
             code = reader._library.cfm_finish(
-                ctypes.byref(reader._layer), routed.shape[0], routed.data_ptr(),
-                latent.data_ptr() if latent is not None else None, out.data_ptr(),
+                ctypes.byref(reader._layer), rows, combined.data_ptr(), out.data_ptr(),
                 ctypes.c_void_p(stream),
             )
         _native.check(code, "cfm_finish")

@@ -56,7 +56,7 @@ _TORCH_TYPES = {
     "starts": torch.int32, "tile_starts": torch.int32, "activations": torch.bfloat16,
     "exact": torch.float32, "down_parts": torch.float32, "encoder_parts": torch.float32,
     "latent": torch.float32, "status": torch.int32, "limbs": torch.int8,
-    "group_offsets": torch.int32, "group_pairs": torch.int32,
+    "group_offsets": torch.int32, "group_pairs": torch.int32, "cuts": torch.int32,
 }
 
 
@@ -118,7 +118,7 @@ class ReaderWorkspace:
             "down_parts": (c, layout.down_tiles, h),
             "encoder_parts": (c, k, layout.encoder_tiles, r), "latent": (c, r),
             "status": (4,), "limbs": (c, blocks, 3, 128),
-            "group_offsets": (experts + 1,), "group_pairs": (c * k,),
+            "group_offsets": (experts + 1,), "group_pairs": (c * k,), "cuts": (c, k + 1),
         }
         for name, shape in shapes.items():
             setattr(self, name, self._view(name, shape))

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 2
+#define CFM_ABI_VERSION 3
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -79,8 +79,11 @@ typedef struct cfm_call {
   int32_t ids_are_int64;  /* ids element type: 0 int32, 1 int64                */
   int32_t weights_are_bf16; /* router weight type: 0 float32, 1 bfloat16       */
   int32_t input_prepared; /* 1: cfm_prepare_input already ran for these rows   */
-  int32_t scores_ready;   /* 1: cfm_select reads `scores` instead of computing */
-  int32_t reserved;
+  int32_t scores_ready;   /* cfm_select: 0 computes the scores, 1 reads `scores`,
+                             2 reads `scores`, takes cut and tie budgets from
+                             `cuts` and keeps local slots only, 3 reads `scores`
+                             and only writes cut and tie budgets to `cuts`      */
+  int32_t row_offset;     /* cfm_select only: first workspace row to process   */
   const void* hidden;     /* bf16 [T, H]                                       */
   const void* ids;        /* [T, K] router expert ids (global ids under EP)    */
   const void* weights;    /* [T, K] router weights                             */
@@ -120,6 +123,7 @@ typedef struct cfm_workspace_layout {
   int64_t limbs;          /* i8  [C, B, 3, 128] base-256 digits of `quantized`  */
   int64_t group_offsets;  /* i32 [E + 1] first pair of every expert             */
   int64_t group_pairs;    /* i32 [C * K] (token, slot) pairs grouped by expert  */
+  int64_t cuts;           /* i32 [C, 1 + K] score cut and per-slot tie budgets   */
   int32_t parts_tokens;   /* tokens the split screen can serve                  */
   int32_t down_tiles;     /* ceil(F / 128) + K - 1                              */
   int32_t encoder_tiles;  /* ceil(I / 256)                                      */
@@ -198,20 +202,20 @@ int cfm_encode(const cfm_layer* layer, void* workspace, int32_t capacity,
 int cfm_output(const cfm_layer* layer, void* workspace, int32_t capacity,
                const cfm_call* call, void* stream);
 
-/* Expert parallelism, owner side: like cfm_output but call->out is f32 [T, H]
- * and receives only the router-weighted sum of this rank's local slots (each
- * expert sum rounded to BF16 first, as in _output); no decoder term.  The
- * caller adds the ranks' partial sums and latents (`latent` of the workspace).
+/* Expert parallelism, owner side: like cfm_output but call->out is f32
+ * [T, H + R]: per row the router-weighted sum of this rank's local slots (each
+ * expert sum rounded to BF16 first, as in _output; no decoder term) followed by
+ * this rank's share of the latent.  The caller adds the rows of all ranks.
  * Replaces: the per-rank part of _output (progressive.py:2019-2111). */
 int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity,
                        const cfm_call* call, void* stream);
 
 /* Expert parallelism, home side: out = bf16(routed + bf16(U bf16(latent))) for
- * `tokens` rows; routed f32 [T, H] and latent f32 [T, R] are the sums over the
- * ranks (latent may be NULL without a recovery map).  Needs only hidden, rank
- * and decoder of `layer`.  Replaces: the tail of _output (:2096-2111). */
-int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* routed, const float* latent,
-               void* out, void* stream);
+ * `tokens` rows of `combined` f32 [T, H + R], the sums over the ranks of the
+ * rows cfm_partial_output wrote.  Needs only hidden, rank and decoder of
+ * `layer`.  Replaces: the tail of _output (:2096-2111). */
+int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined, void* out,
+               void* stream);
 
 /* The whole layer on one stream: prepare (unless input_prepared), route,
  * screen, select, exact, down, encode, output.  Single-device readers only;

@@ -72,6 +72,8 @@ typedef struct oracle_result {
                              decoder term and the final rounding, or NULL */
   const float* given_scores; /* [T, N] scores to select by instead of the computed ones
                                 (expert parallelism: sums over ranks), or NULL */
+  const uint8_t* given_selected; /* [T, N] kept-channel mask to use instead of selecting
+                                    (expert parallelism: a rank's own slots), or NULL */
 } oracle_result;
 
 /* ---- number formats ---------------------------------------------------- */
@@ -360,7 +362,12 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
 
   /* select: F best, ties to the lower candidate index */
   int32_t* kept = (int32_t*)malloc(sizeof(int32_t) * F);
-  if (screened) {
+  if (out->given_selected) {
+    int count = 0;
+    for (int i = 0; i < F; ++i) kept[i] = -1;
+    for (int i = 0; i < N && count < F; ++i)
+      if (out->given_selected[(int64_t)t * N + i]) kept[count++] = i;
+  } else if (screened) {
     ranked* order_by_score = (ranked*)malloc(sizeof(ranked) * N);
     for (int i = 0; i < N; ++i) {
       memcpy(&order_by_score[i].key, &score[i], 4);
@@ -373,7 +380,8 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
   } else {
     for (int i = 0; i < F; ++i) kept[i] = i;
   }
-  for (int i = 0; i < F; ++i) chosen[kept[i]] = 1;
+  for (int i = 0; i < F; ++i)
+    if (kept[i] >= 0) chosen[kept[i]] = 1;
   if (out->candidate_ids) memcpy(out->candidate_ids + (int64_t)t * F, kept, sizeof(int32_t) * F);
   if (out->selected) memcpy(out->selected + (int64_t)t * N, chosen, (size_t)N);
 

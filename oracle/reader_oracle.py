@@ -60,6 +60,7 @@ class _Result(ctypes.Structure):
             "output",
             "routed",
             "given_scores",
+            "given_selected",
         )
     ]
 
@@ -127,6 +128,7 @@ def forward(
     fp32: bool = False,
     threads: int | None = None,
     given_scores: Tensor | None = None,
+    given_selected: Tensor | None = None,
 ) -> dict[str, Tensor]:
     """Run the oracle on T tokens.
 
@@ -137,8 +139,9 @@ def forward(
     the latent and the output (`[T, H]` FP32 holding BF16-rounded values, or the
     unrounded FP32 evaluation with `fp32=True`).  `given_scores` `[T, N]` replaces
     the computed scores for the selection (expert parallelism: the sum over
-    ranks); `routed` in the result is the FP32 router-weighted sum of the local
-    slots before the decoder term.
+    ranks); `given_selected` `[T, N]` is a kept-channel mask used instead of any
+    selection; `routed` in the result is the FP32 router-weighted sum of the
+    local slots before the decoder term.
     """
     lib = load()
     h, i, k = plan.hidden_size, plan.expert_width, plan.top_k
@@ -188,9 +191,11 @@ def forward(
         "routed": torch.zeros(tokens, h),
     }
     given = _cpu(given_scores, torch.float32) if given_scores is not None else None
+    mask = _cpu(given_selected, torch.uint8) if given_selected is not None else None
     result = _Result(
-        *(out[name].data_ptr() for name, _ in _Result._fields_[:-1]),
+        *(out[name].data_ptr() for name, _ in _Result._fields_[:-2]),
         given.data_ptr() if given is not None else None,
+        mask.data_ptr() if mask is not None else None,
     )
     if threads is None:
         threads = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)

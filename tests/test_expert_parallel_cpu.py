@@ -45,17 +45,60 @@ class OracleEngine:
 
     def screen(self, hidden, ids, weights, padding):
         self.inputs = dict(hidden=hidden, ids=ids, weights=weights, padding=padding)
-        return self.oracle.forward(**self.fixed, **self.inputs)["scores"].clone()
+        out = self.oracle.forward(**self.fixed, **self.inputs)
+        self.scores = out["scores"].clone()
+        self.local_ids = out["sorted_ids"]
+        k = self.case.plan.top_k
+        self.cuts = torch.zeros(hidden.shape[0], k + 1, dtype=torch.int32)
+        return self.scores
 
-    def local(self, scores):
-        out = self.oracle.forward(**self.fixed, **self.inputs, given_scores=scores)
-        self.selected = out["selected"]
-        latent = out["latent"] if self.case.decoder is not None else None
-        return out["routed"], latent
+    def find_cuts(self, first_row, rows):
+        """The cut of each home token from its summed scores: F-th largest key and tie budgets."""
+        plan = self.case.plan
+        f, k, i = plan.final_count, plan.top_k, plan.expert_width
+        for row in range(first_row, first_row + rows):
+            keys = self.scores[row].view(torch.int32).long()
+            if f == plan.candidate_count:
+                continue
+            order = torch.argsort(keys, descending=True, stable=True)[:f]
+            cut = int(keys[order[-1]])
+            kept_ties = (keys[order] == cut).nonzero().flatten()
+            tie_slots = order[kept_ties] // i
+            self.cuts[row, 0] = cut
+            for slot in range(k):
+                self.cuts[row, 1 + slot] = int((tie_slots == slot).sum())
+        return self.cuts
 
-    def finish(self, routed, latent):
+    def local(self):
+        plan = self.case.plan
+        k, i, n = plan.top_k, plan.expert_width, plan.candidate_count
+        rows = self.scores.shape[0]
+        mask = torch.zeros(rows, n, dtype=torch.bool)
+        keys = self.scores.view(torch.int32).long().reshape(rows, k, i)
+        for row in range(rows):
+            for slot in range(k):
+                if self.local_ids[row, slot] < 0:
+                    continue
+                if plan.final_count == n:
+                    mask[row, slot * i : (slot + 1) * i] = True
+                    continue
+                cut, budget = int(self.cuts[row, 0]), int(self.cuts[row, 1 + slot])
+                above = keys[row, slot] > cut
+                tied = keys[row, slot] == cut
+                tied &= tied.cumsum(0) <= budget
+                mask[row, slot * i : (slot + 1) * i] = above | tied
+        out = self.oracle.forward(**self.fixed, **self.inputs, given_selected=mask)
+        self.selected = mask
+        rank = self.case.decoder.shape[1] if self.case.decoder is not None else 0
+        if rank:
+            return torch.cat((out["routed"], out["latent"]), dim=1)
+        return out["routed"]
+
+    def finish(self, combined):
+        h = self.case.plan.hidden_size
+        routed, latent = combined[:, :h], combined[:, h:]
         correction = 0.0
-        if latent is not None:
+        if latent.shape[1]:
             z = latent.bfloat16().float()
             correction = (self.case.decoder.float() @ z.T).T.bfloat16().float()
         return (routed + correction).bfloat16()
@@ -85,7 +128,7 @@ def _worker(rank, world, port, name, results):
         out = expert_parallel_forward(
             engine, case.hidden[rows], case.ids[rows], case.weights[rows], padding
         )
-        results[rank] = (out.float(), engine.selected)
+        results[rank] = (out.float(), engine.selected, engine.local_ids)
     finally:
         dist.destroy_process_group()
 
@@ -104,10 +147,12 @@ def test_two_rank_expert_parallel_matches_single_process(oracle, name):
     if case.padding is not None:
         active = ~case.padding
     for rank in range(world):
-        out, selected = results[rank]
+        out, selected, local_ids = results[rank]
         rows = slice(rank * tokens, (rank + 1) * tokens)
-        # Every rank kept the same channels for every token, equal to the single-process result.
-        assert torch.equal(selected[active], want["selected"][active])
+        # Each rank kept, in its own slots, exactly the channels the single-process run kept.
+        i = case.plan.expert_width
+        mine = (local_ids >= 0).repeat_interleave(i, dim=1)
+        assert torch.equal(selected[active], (want["selected"] & mine)[active])
         torch.testing.assert_close(out[active[rows]], want["output"][rows][active[rows]],
                                    rtol=0.016, atol=2e-3)
         assert not out[~active[rows]].any()

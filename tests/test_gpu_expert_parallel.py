@@ -66,8 +66,9 @@ def _worker(rank, world, port, name, results):
                       case.weights[rows].to(device), padding)
         torch.cuda.synchronize()
         total = world * tokens
-        kept = sharded.reader.candidate_ids[-1][:total].cpu()
-        scores = sharded.reader.scores[0][:total].cpu()
+        kept = sharded.reader.selected[:total].cpu()
+        kept_local = (sharded.reader.ids[:total].cpu() >= 0)
+        scores = sharded.reader.scores[0][rows].cpu()  # summed on the home rank only
 
         # Reference-compatible mode: replicated tokens, all-reduce inside the reader.
         replicated = ProgressiveReader(
@@ -100,8 +101,9 @@ def _worker(rank, world, port, name, results):
                              case.weights.to(device), all_padding)
             torch.cuda.synchronize()
             expected = (reference.float().cpu(), full.candidate_ids[-1][:total].cpu(),
-                        full.scores[0][:total].cpu())
-        results[rank] = (out.float().cpu(), kept, scores, partial.cpu(), compat_kept, expected)
+                        full.scores[0][:total].cpu(), full.selected[:total].cpu())
+        results[rank] = (out.float().cpu(), kept, kept_local, scores, partial.cpu(),
+                         compat_kept, expected)
     finally:
         dist.destroy_process_group()
 
@@ -116,18 +118,21 @@ def test_sharded_reader_matches_single_gpu(name):
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), name, results), nprocs=world, join=True)
     case = prepared(name)["case"]
-    reference, kept, scores = results[0][5]
+    reference, kept, scores, selected = results[0][6]
     tokens = case.hidden.shape[0] // world
+    width = case.plan.expert_width
     active = torch.ones(case.hidden.shape[0], dtype=torch.bool)
     if case.padding is not None:
         active = ~case.padding
     envelope = 2 * torch.finfo(torch.bfloat16).eps * reference.abs().max().item()
     for rank in range(world):
-        out, rank_kept, rank_scores, compat, compat_kept, _ = results[rank]
+        out, rank_kept, rank_local, home_scores, compat, compat_kept, _ = results[rank]
         rows = slice(rank * tokens, (rank + 1) * tokens)
-        # Summed scores and kept channels equal the single-GPU reader's, bit for bit.
-        assert torch.equal(rank_scores[active], scores[active])
-        assert torch.equal(rank_kept[active], kept[active])
+        # Summed scores of the home tokens equal the single-GPU reader's, bit for bit ...
+        assert torch.equal(home_scores[active[rows]], scores[rows][active[rows]])
+        # ... and every rank keeps, in its own slots, exactly the single-GPU reader's channels.
+        mine = rank_local.repeat_interleave(width, dim=1)
+        assert torch.equal(rank_kept[active], (selected & mine)[active])
         assert torch.equal(compat_kept[active], kept[active])
         torch.testing.assert_close(out[active[rows]], reference[rows][active[rows]],
                                    rtol=0, atol=envelope)
