@@ -21,6 +21,7 @@
 
 #include "cfm_b200.h"
 
+#include <algorithm>
 #include <mutex>
 
 namespace cfm {
@@ -572,7 +573,7 @@ struct GroupFetch {
   int exponent[2];       // of the two tokens this lane finishes (2 tq, 2 tq + 1)
 };
 
-// grid (ceil(2I / 128), E), 256 threads, no shared memory, no barrier.  A warp
+// grid (ceil(2I / 128), E, passes), 256 threads, no shared memory, no barrier.  A warp
 // owns 16 sketch rows of one expert and walks the rotation blocks in order.  Per
 // block it decodes 16 rows x 128 coordinates into int8 fragments and multiplies
 // them with the int8 digits of up to eight of the expert's tokens (m16n8k32,
@@ -582,7 +583,7 @@ struct GroupFetch {
 // come straight from global memory (L1/L2 resident, 32 contiguous bytes per
 // lane and digit).  The next block's words, digits, scales and exponents are
 // in flight in registers while the current block computes.  Experts with more
-// than eight tokens take further passes of eight.
+// than eight tokens take further passes of eight, spread over grid.z.
 __global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Workspace ws) {
   const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -597,7 +598,7 @@ __global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Wo
   const size_t sketch_b = (static_cast<size_t>(e) * L.B * rows + row_b) * (kBlock / 32);
   const __half* scales = L.statistics + static_cast<size_t>(e) * L.B * 2 * rows;
 
-  for (int base = 0; base < total; base += 8) {
+  for (int base = 8 * blockIdx.z; base < total; base += 8 * gridDim.z) {
     const int count = min(8, total - base);
     // Pair of the token whose digits this lane feeds (column g of the tiles).
     const int pair_g = g < count ? ws.group_pairs[first + base + g] : -1;
@@ -831,51 +832,59 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     *total = sum;
     return before;
   };
-  int ties = 0;
+  // Counts above the cut and tied with it, packed into one scan (N < 65536).
+  const bool budgets = cut_given || cut_only;
+  int counted = 0;
   if (screened)
-    for (int i = begin; i < end; ++i) ties += keys[i] == cut;
-  int all_ties = 0;
-  const int ties_before = block_exclusive(ties, &all_ties);
-  {
+    for (int i = begin; i < end; ++i) {
+      const uint32_t k = keys[i];
+      counted += (k > cut ? 0x10000 : 0) + (k == cut ? 1 : 0);
+    }
+  int all_counted = 0;
+  const int counted_before = block_exclusive(counted, &all_counted);
+  const int ties_before = counted_before & 0xffff, above_before = counted_before >> 16;
+  if (budgets) {
     int running = ties_before;
     for (int i = begin; i < end; ++i) {
       if (i % I == 0) s_tie_start[i / I] = running;
       running += screened && keys[i] == cut;
     }
-    if (tid == 0) s_tie_start[K] = all_ties;
-  }
-  __syncthreads();
-  if (tid < K) {
-    int budget;
-    if (cut_given) {
-      budget = cuts[1 + tid];
-    } else {
-      const int in_slot = s_tie_start[tid + 1] - s_tie_start[tid];
-      budget = max(0, min(in_slot, take_ties - s_tie_start[tid]));
-      cuts[1 + tid] = budget;
-      if (tid == 0) cuts[0] = static_cast<int32_t>(cut);
+    if (tid == 0) s_tie_start[K] = all_counted & 0xffff;
+    __syncthreads();
+    if (tid < K) {
+      int budget;
+      if (cut_given) {
+        budget = cuts[1 + tid];
+      } else {
+        const int in_slot = s_tie_start[tid + 1] - s_tie_start[tid];
+        budget = max(0, min(in_slot, take_ties - s_tie_start[tid]));
+        cuts[1 + tid] = budget;
+        if (tid == 0) cuts[0] = static_cast<int32_t>(cut);
+      }
+      s_budget[tid] = budget;
     }
-    s_budget[tid] = budget;
+    if (cut_only) return;  // the token's home rank only publishes the cut and the budgets
+    __syncthreads();
   }
-  if (cut_only) return;  // the token's home rank only publishes the cut and the budgets
-  __syncthreads();
   auto keeps = [&](int i, int running) {
     const int slot = i / I;
     if (cut_given && route[slot] < 0) return false;  // another rank's slot
     if (!screened) return true;
     const uint32_t k = keys[i];
-    return k > cut || (k == cut && running - s_tie_start[slot] < s_budget[slot]);
+    if (k != cut) return k > cut;
+    return budgets ? running - s_tie_start[slot] < s_budget[slot] : running < take_ties;
   };
-  int kept = 0;
-  {
-    int running = ties_before;
+  int total_kept = F;
+  int position = above_before + min(ties_before, take_ties);
+  if (!screened) position = begin;
+  if (budgets) {
+    int kept = 0, running = ties_before;
     for (int i = begin; i < end; ++i) {
       kept += keeps(i, running);
       running += screened && keys[i] == cut;
     }
+    position = block_exclusive(kept, &total_kept);
   }
-  int total_kept = 0;
-  int position = block_exclusive(kept, &total_kept);
   uint8_t* selected = ws.selected + static_cast<size_t>(t) * N;
   uint8_t* completed = ws.completed + static_cast<size_t>(t) * N;
   int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * F;
@@ -971,28 +980,34 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
   extern __shared__ uint4 xs[];  // H bf16 values of the token
   const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (padding && padding[t]) return;
+  const int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * L.F;
+  const bool strided = gridDim.x * kExactWarps < L.F;  // CTAs walk the list in strides
   if (L.expert_map) {
-    // Expert parallel: leave before staging the input when none of this CTA's
-    // candidates belongs to a local expert (most do not).
-    const int probe = blockIdx.x * kExactWarps + warp;
-    bool mine = false;
-    if (probe < L.F) {
-      const int cid = ws.candidate_ids[static_cast<size_t>(t) * L.F + probe];
-      mine = cid >= 0 && ws.ids[static_cast<size_t>(t) * L.K + cid / L.I] >= 0;
+    // Expert parallel: leave before staging the input when this CTA has nothing
+    // to do.  A list cut down to the local slots ends with -1 entries; a full list
+    // is probed for candidates of local experts.
+    if (list[blockIdx.x * kExactWarps] < 0) return;
+    if (!strided) {
+      const int probe = blockIdx.x * kExactWarps + warp;
+      bool mine = false;
+      if (probe < L.F) {
+        const int cid = list[probe];
+        mine = cid >= 0 && ws.ids[static_cast<size_t>(t) * L.K + cid / L.I] >= 0;
+      }
+      if (!__syncthreads_or(mine)) return;
     }
-    if (!__syncthreads_or(mine)) return;
   }
   const int chunks = L.H / 8;
   const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
   for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
   __syncthreads();
-  const int index = blockIdx.x * kExactWarps + warp;
-  if (index >= L.F) return;
-  const int cid = ws.candidate_ids[static_cast<size_t>(t) * L.F + index];
-  if (cid < 0) return;
+  for (int index = blockIdx.x * kExactWarps + warp; index < L.F;
+       index += gridDim.x * kExactWarps) {
+  const int cid = list[index];
+  if (cid < 0) break;  // lists end with -1 entries
   const int slot = cid / L.I, c = cid - slot * L.I;
   const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
-  if (e < 0) return;
+  if (e < 0) continue;
   const uint4* gate = reinterpret_cast<const uint4*>(
       L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
   const uint4* up = gate + static_cast<size_t>(L.I) * L.H / 8;
@@ -1051,6 +1066,7 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
     ws.exact[static_cast<size_t>(t) * 2 * L.F + index] = g;
     ws.exact[static_cast<size_t>(t) * 2 * L.F + L.F + index] = u;
   }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1071,6 +1087,13 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
   const int t = blockIdx.z, tile = blockIdx.y, tid = threadIdx.x;
   if (padding && padding[t]) return;
   const size_t token_pairs = static_cast<size_t>(t) * L.K;
+  {
+    // Tiles are laid out slot after slot; leave at once beyond the last one.
+    const size_t last = token_pairs + L.K - 1;
+    const int tail =
+        ws.ids[last] >= 0 ? (ws.counts[last] + kDownTileRows - 1) / kDownTileRows : 0;
+    if (tile >= ws.tile_starts[last] + tail) return;
+  }
   if (tid == 0) s_slot = -1;
   __syncthreads();
   if (tid < L.K) {  // the slot whose tile range holds this tile, if any
@@ -1501,7 +1524,11 @@ static int run_screen_grouped(const Bound& b) {
   k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
   int rc = launched();
   if (rc) return rc;
-  const dim3 grid((2 * b.L.I + kGroupRows - 1) / kGroupRows, b.L.E);
+  // Experts with many tokens (few local experts under expert parallelism) spread
+  // their passes of eight tokens over grid.z.
+  const int64_t per_expert = (static_cast<int64_t>(b.T) * b.L.K + b.L.E - 1) / b.L.E;
+  const int passes = static_cast<int>(std::min<int64_t>(8, std::max<int64_t>(1, (per_expert + 7) / 8)));
+  const dim3 grid((2 * b.L.I + kGroupRows - 1) / kGroupRows, b.L.E, passes);
   k_screen_grouped<<<grid, kGroupThreads, 0, b.stream>>>(b.L, b.ws);
   if ((rc = launched())) return rc;
   if (b.padding || b.L.expert_map) {
@@ -1563,7 +1590,15 @@ static int run_exact(const Bound& b, const cfm_call* call) {
         k_exact, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);
   }
-  k_exact<<<dim3((b.L.F + kExactWarps - 1) / kExactWarps, b.T), kExactWarps * 32, smem,
+  int ctas = (b.L.F + kExactWarps - 1) / kExactWarps;
+  if (b.L.expert_map && b.L.global_experts > 0) {
+    // Expert parallel: a rank holds E of the global experts, so about that share
+    // of a token's kept channels; CTAs stride through the list, twice the
+    // expected share of them are launched.
+    const int64_t share = (2LL * ctas * b.L.E + b.L.global_experts - 1) / b.L.global_experts;
+    ctas = static_cast<int>(std::max<int64_t>(8, std::min<int64_t>(ctas, share)));
+  }
+  k_exact<<<dim3(ctas, b.T), kExactWarps * 32, smem,
             b.stream>>>(b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden), b.padding);
   return launched();
 }
