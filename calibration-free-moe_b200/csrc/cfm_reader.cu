@@ -634,10 +634,7 @@ __global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Wo
     };
 
     float run[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    GroupFetch next = fetch(0);
-    for (int b = 0; b < L.B; ++b) {
-      const GroupFetch cur = next;
-      if (b + 1 < L.B) next = fetch(b + 1);
+    auto compute = [&](const GroupFetch& cur) {
       uint32_t fa[8], fb[8];
       decode_word(cur.word_a.x, fa[0], fa[1], fa[2], fa[3]);
       decode_word(cur.word_a.y, fa[4], fa[5], fa[6], fa[7]);
@@ -661,6 +658,15 @@ __global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Wo
         const float d = __fmul_rn(__int2float_rn(dot), unscale);
         run[i] = __fadd_rn(run[i], __fmul_rn(i < 2 ? scale_a : scale_b, d));
       }
+    };
+    // Two fetch buffers used in turn, so that no block's data is copied between
+    // registers: while one block computes the next one's loads are in flight.
+    GroupFetch even = fetch(0), odd;
+    for (int b = 0; b < L.B; b += 2) {
+      if (b + 1 < L.B) odd = fetch(b + 1);
+      compute(even);
+      if (b + 2 < L.B) even = fetch(b + 2);
+      if (b + 1 < L.B) compute(odd);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
