@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 3
+ABI_VERSION = 4
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -86,7 +86,7 @@ _LAYOUT_ARRAYS = (
     "ids", "weights", "norms", "planes", "coordinates", "quantized", "exponents", "parts",
     "counters", "partial", "scores", "selected", "completed", "candidate_ids", "counts",
     "starts", "tile_starts", "activations", "exact", "down_parts", "encoder_parts", "latent",
-    "status", "limbs", "group_offsets", "group_pairs", "cuts",
+    "status", "limbs", "group_offsets", "group_pairs", "cuts", "variances",
 )
 
 

@@ -91,6 +91,36 @@ __device__ __forceinline__ float point_score(float g, float u, float norm, float
   return __fadd_rn(__fmul_rn(__fmul_rn(t, t), __fmul_rn(w, w)), 0.0f);
 }
 
+// Recovery-aware score: w^2 times the expected squared output error of skipping
+// the channel, with the gate modelled as Gaussian around g (five Gauss-Hermite
+// nodes), sketch residual variances vg and vu, down-column norm n and the
+// recovery response split into alpha (along the down column) and beta (across):
+//   n^2 max(E[a^2] - E[a]^2, 0) + ((n E[a] - alpha p)^2 + (beta p)^2),
+// p = bf16(phi(g) u), on BF16-rounded projections.
+__device__ __forceinline__ float risk_score(float g, float u, float vg, float vu, float norm,
+                                            float alpha, float beta, float w, int activation) {
+  const float gb = bf16_round(g), ub = bf16_round(u);
+  const float sg = __fsqrt_rn(vg), su = __fsqrt_rn(vu);
+  const float spread = __fadd_rn(__fmul_rn(ub, ub), __fmul_rn(su, su));
+  const float nodes[5] = {-2.85697007f, -1.35562618f, 0.0f, 1.35562618f, 2.85697007f};
+  const float mass[5] = {0.0112574113f, 0.222075922f, 0.533333333f, 0.222075922f,
+                         0.0112574113f};
+  float mu = 0.0f, second = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 5; ++j) {
+    const float a = pinned_activate(__fadd_rn(gb, __fmul_rn(nodes[j], sg)), activation);
+    mu = __fadd_rn(mu, __fmul_rn(__fmul_rn(mass[j], a), ub));
+    second = __fadd_rn(second, __fmul_rn(__fmul_rn(mass[j], __fmul_rn(a, a)), spread));
+  }
+  const float p = bf16_round(__fmul_rn(pinned_activate(gb, activation), ub));
+  const float spread_error = fmaxf(__fsub_rn(second, __fmul_rn(mu, mu)), 0.0f);
+  float risk = __fmul_rn(__fmul_rn(norm, norm), spread_error);
+  const float along = __fsub_rn(__fmul_rn(norm, mu), __fmul_rn(alpha, p));
+  const float across = __fmul_rn(beta, p);
+  risk = __fadd_rn(risk, __fadd_rn(__fmul_rn(along, along), __fmul_rn(across, across)));
+  return __fadd_rn(__fmul_rn(risk, __fmul_rn(w, w)), 0.0f);
+}
+
 // 16-byte read-only load that does not allocate in L1 (streamed weights).
 __device__ __forceinline__ uint4 load_stream16(const void* p) {
   uint4 v;

@@ -57,6 +57,7 @@ struct Workspace {
   int32_t* group_offsets;
   int32_t* group_pairs;
   int32_t* cuts;
+  float* variances;
   int32_t parts_tokens;
   int32_t down_tiles;
   int32_t encoder_tiles;
@@ -79,6 +80,10 @@ struct Layer {  // device-visible copy of cfm_layer with typed pointers
   const int32_t* expert_map;
   double* read_work;
 };
+
+// Score of candidate i (slot's channel c of local expert e) of token t; defined with the select kernel.
+__device__ __forceinline__ float candidate_score(const Layer& L, const Workspace& ws, int t, int i,
+                                                 int e, int c, float weight);
 
 static int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
@@ -129,6 +134,7 @@ static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layou
   o->group_offsets = take(4 * (static_cast<int64_t>(l->experts > 0 ? l->experts : 1) + 1));
   o->group_pairs = take(4 * C * K);
   o->cuts = take(4 * C * (K + 1));
+  o->variances = take(4 * C * 2 * N);
   o->bytes = at;
   return 0;
 }
@@ -163,6 +169,7 @@ static Workspace bind(const cfm_workspace_layout& o, void* base, int32_t capacit
   w.group_offsets = reinterpret_cast<int32_t*>(p + o.group_offsets);
   w.group_pairs = reinterpret_cast<int32_t*>(p + o.group_pairs);
   w.cuts = reinterpret_cast<int32_t*>(p + o.cuts);
+  w.variances = reinterpret_cast<float*>(p + o.variances);
   w.parts_tokens = o.parts_tokens;
   w.down_tiles = o.down_tiles;
   w.encoder_tiles = o.encoder_tiles;
@@ -292,20 +299,18 @@ __global__ void __launch_bounds__(kBlock) k_prepare(Layer L, Workspace ws,
   }
   int qsum = q;
 #pragma unroll
-  for (int w = 16; w; w >>= 1) {
-    qsum += __shfl_xor_sync(kFull, qsum, w);
-    energy = __fadd_rn(energy, __shfl_xor_sync(kFull, energy, w));
-  }
-  if (lane == 0) {
-    warp_i[warp] = qsum;
-    warp_f[warp] = energy;
-  }
+  for (int w = 16; w; w >>= 1) qsum += __shfl_xor_sync(kFull, qsum, w);
+  if (lane == 0) warp_i[warp] = qsum;
+  sm[c] = energy;  // squares of the kept values, zero elsewhere
   __syncthreads();
   if (c == 0) {
     const size_t row = static_cast<size_t>(t) * L.B + b;
     ws.exponents[2 * row] = e;
     ws.exponents[2 * row + 1] = warp_i[0] + warp_i[1] + warp_i[2] + warp_i[3];
-    ws.norms[row] = __fadd_rn(__fadd_rn(warp_f[0], warp_f[1]), __fadd_rn(warp_f[2], warp_f[3]));
+    // Energy of the kept coordinates, summed in coordinate order (pinned).
+    float total = 0.0f;
+    for (int j = 0; j < kBlock; ++j) total = __fadd_rn(total, sm[j]);
+    ws.norms[row] = total;
   }
 }
 
@@ -700,12 +705,47 @@ __global__ void k_score(Layer L, Workspace ws, const uint8_t* padding) {
   const int slot = i / L.I, c = i - slot * L.I;
   const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
   float value = 0.0f;
-  if (e >= 0 && !(padding && padding[t])) {
-    const float* gate = ws.partial + static_cast<size_t>(t) * 2 * L.N;
-    value = point_score(gate[i], gate[L.N + i], L.norms[static_cast<size_t>(e) * L.I + c],
-                        ws.weights[static_cast<size_t>(t) * L.K + slot], L.activation);
-  }
+  if (e >= 0 && !(padding && padding[t]))
+    value = candidate_score(L, ws, t, i, e, c, ws.weights[static_cast<size_t>(t) * L.K + slot]);
   ws.scores[static_cast<size_t>(t) * L.N + i] = value;
+}
+
+// Residual variance of every candidate's sketch projections (recovery-aware
+// score): sum over blocks, in block order, of the row's FP16 residual variance
+// times the energy of the token's kept coordinates in that block.
+// grid (T*K pairs, ceil(2I / 256)), 256 threads, one sketch row per thread.
+__global__ void __launch_bounds__(256) k_variance(Layer L, Workspace ws, const uint8_t* padding) {
+  const int pair = blockIdx.x, row = blockIdx.y * 256 + threadIdx.x;
+  const int rows = 2 * L.I;
+  if (row >= rows) return;
+  const int t = pair / L.K, slot = pair - t * L.K;
+  const int e = ws.ids[pair];
+  float sum = 0.0f;
+  if (e >= 0 && !(padding && padding[t])) {
+    const __half* variance = L.statistics + (static_cast<size_t>(e) * L.B * 2 + 1) * rows + row;
+    const float* energy = ws.norms + static_cast<size_t>(t) * L.B;
+    for (int b = 0; b < L.B; ++b)
+      sum = __fadd_rn(sum, __fmul_rn(__half2float(variance[static_cast<size_t>(b) * 2 * rows]),
+                                     energy[b]));
+  }
+  float* out = ws.variances + static_cast<size_t>(t) * 2 * L.N + static_cast<size_t>(slot) * L.I;
+  (row < L.I ? out[row] : out[L.N + row - L.I]) = sum;
+}
+
+// Score of candidate i of token t from its projections (and variances).
+__device__ __forceinline__ float candidate_score(const Layer& L, const Workspace& ws, int t, int i,
+                                                 int e, int c, float weight) {
+  const float* gate = ws.partial + static_cast<size_t>(t) * 2 * L.N;
+  const float norm = L.norms[static_cast<size_t>(e) * L.I + c];
+  if (L.score == CFM_SCORE_POINT) return point_score(gate[i], gate[L.N + i], norm, weight, L.activation);
+  const float* variance = ws.variances + static_cast<size_t>(t) * 2 * L.N;
+  float alpha = 0.0f, beta = 0.0f;
+  if (L.geometry) {
+    alpha = L.geometry[(static_cast<size_t>(e) * L.I + c) * 2];
+    beta = L.geometry[(static_cast<size_t>(e) * L.I + c) * 2 + 1];
+  }
+  return risk_score(gate[i], gate[L.N + i], variance[i], variance[L.N + i], norm, alpha, beta,
+                    weight, L.activation);
 }
 
 // ---------------------------------------------------------------------------
@@ -744,14 +784,12 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
       for (int i = tid; i < N; i += kSelectThreads) keys[i] = __float_as_uint(score[i]);
     } else {
       // Score every candidate from its sketch projections (zero for remote slots).
-      const float* gate = ws.partial + static_cast<size_t>(t) * 2 * N;
       for (int i = tid; i < N; i += kSelectThreads) {
         const int slot = i / I, c = i - slot * I;
         const int e = ws.ids[static_cast<size_t>(t) * K + slot];
         float value = 0.0f;
         if (e >= 0)
-          value = point_score(gate[i], gate[N + i], L.norms[static_cast<size_t>(e) * I + c],
-                              ws.weights[static_cast<size_t>(t) * K + slot], L.activation);
+          value = candidate_score(L, ws, t, i, e, c, ws.weights[static_cast<size_t>(t) * K + slot]);
         score[i] = value;
         keys[i] = __float_as_uint(value);
       }
@@ -1479,7 +1517,8 @@ static int bind_call(const cfm_layer* layer, void* workspace, int32_t capacity,
   if (layer->experts < 1 || !layer->gate_up || !layer->down) return CFM_E_NULL;
   if (layer->activation != CFM_ACT_SILU && layer->activation != CFM_ACT_GELU_TANH)
     return CFM_E_UNSUPPORTED;
-  if (layer->score != CFM_SCORE_POINT) return CFM_E_UNSUPPORTED;
+  if (layer->score != CFM_SCORE_POINT && layer->score != CFM_SCORE_RECOVERY_AWARE)
+    return CFM_E_UNSUPPORTED;
   const bool screened = layer->final_count < layer->top_k * layer->width;
   if (screened && (!layer->sketch || !layer->statistics || !layer->norms || !layer->signs))
     return CFM_E_NULL;
@@ -1547,8 +1586,20 @@ static int run_screen_grouped(const Bound& b) {
 // Batch size from which the screen runs expert-major on the tensor cores.
 constexpr int kGroupedScreenTokens = 8;
 
+static int run_screen_projections(const Bound& b);
+
 static int run_screen(const Bound& b) {
   if (b.L.F >= b.L.N) return 0;
+  if (b.L.score == CFM_SCORE_RECOVERY_AWARE) {
+    k_variance<<<dim3(b.T * b.L.K, (2 * b.L.I + 255) / 256), 256, 0, b.stream>>>(b.L, b.ws,
+                                                                                 b.padding);
+    const int rc = launched();
+    if (rc) return rc;
+  }
+  return run_screen_projections(b);
+}
+
+static int run_screen_projections(const Bound& b) {
   if (b.L.sketch_grouped && b.T >= kGroupedScreenTokens && b.L.E <= 4096)
     return run_screen_grouped(b);
   // Split the rotation blocks across CTAs while the batch is too small to fill

@@ -47,6 +47,30 @@ def channel_major_down(weight: Tensor) -> Tensor:
     return weight.transpose(1, 2).contiguous().transpose(1, 2)
 
 
+def recovery_geometry(down: Tensor, encoder: Tensor, decoder: Tensor, norms: Tensor) -> Tensor:
+    """Split every channel's recovery response U B_c along and across its down column.
+
+    down is the channel-major down weight (logical `[E, H, I]`), encoder the
+    transposed encoder `[E, I, R]`, decoder `[H, R]`, norms the down-column norms
+    `[E, I]`.  Returns FP32 `[E, I, 2]`: alpha = <d_c, U B_c> / ||d_c|| (1 in
+    place of a zero norm) and beta = sqrt(max(||U B_c||^2 - alpha^2, 0)); one
+    expert at a time, nothing of the expanded response is kept
+    (reference progressive.py:3359-3373).
+    """
+    experts, _, width = down.shape
+    geometry = torch.zeros((experts, width, 2), device=down.device, dtype=torch.float32)
+    decoder_rows = decoder.float().T
+    for expert in range(experts):
+        column = down[expert].float().T  # [I, H]
+        response = encoder[expert].float() @ decoder_rows  # [I, H]
+        norm = norms[expert]
+        alpha = (column * response).sum(-1) / torch.where(norm > 0, norm, torch.ones_like(norm))
+        beta = (response.square().sum(-1) - alpha.square()).clamp_min(0).sqrt()
+        geometry[expert, :, 0] = alpha
+        geometry[expert, :, 1] = beta
+    return geometry
+
+
 _TORCH_TYPES = {
     "ids": torch.int32, "weights": torch.float32, "norms": torch.float32,
     "planes": torch.float32, "coordinates": torch.int32, "quantized": torch.int32,
@@ -57,6 +81,7 @@ _TORCH_TYPES = {
     "exact": torch.float32, "down_parts": torch.float32, "encoder_parts": torch.float32,
     "latent": torch.float32, "status": torch.int32, "limbs": torch.int8,
     "group_offsets": torch.int32, "group_pairs": torch.int32, "cuts": torch.int32,
+    "variances": torch.float32,
 }
 
 
@@ -119,6 +144,7 @@ class ReaderWorkspace:
             "encoder_parts": (c, k, layout.encoder_tiles, r), "latent": (c, r),
             "status": (4,), "limbs": (c, blocks, 3, 128),
             "group_offsets": (experts + 1,), "group_pairs": (c * k,), "cuts": (c, k + 1),
+            "variances": (c, 2, n),
         }
         for name, shape in shapes.items():
             setattr(self, name, self._view(name, shape))
@@ -202,8 +228,6 @@ class ProgressiveReader:
             raise ValueError("selection_threshold mode is not provided by this build")
         if selection_score not in SCORE_CODES:
             raise ValueError("selection_score must be 'recovery-aware' or 'point'")
-        if selection_score != "point":
-            raise ValueError("This build provides the 'point' selection score only")
         if activation not in ACTIVATION_CODES:
             raise ValueError(f"Unsupported routed expert activation: {activation}")
         if screen_block_splits not in (1, 2, 4, 8) or grouped_screen_splits not in (1, 2, 4, 8):
@@ -295,6 +319,8 @@ class ProgressiveReader:
                 encoder.to(device=device, dtype=torch.bfloat16).transpose(1, 2).contiguous()
             )
             self.decoder = decoder.to(device=device, dtype=torch.bfloat16).contiguous()
+            if selection_score != "point":
+                self.recovery_geometry = recovery_geometry(self.down, self.encoder, self.decoder, self.norms)
 
         if workspace is None:
             workspace = ReaderWorkspace(
@@ -306,6 +332,7 @@ class ProgressiveReader:
         self.workspace = workspace
         w = workspace
         self.ids, self.weights, self.partial = w.ids, w.weights, w.partial
+        self.variances, self.norms_input = w.variances, w.norms
         self.sketch_planes, self.sketch_coordinates = w.sketch_planes, w.sketch_coordinates
         self.screen_parts, self.screen_counters = w.screen_parts, w.screen_counters
         self.activations, self.completed, self.selected = w.activations, w.completed, w.selected
@@ -318,10 +345,11 @@ class ProgressiveReader:
         )
         self.workspace_bytes = 0 if w.charged else w.bytes
         w.charged = True
-        self.recovery_geometry_bytes = 0
-        self.recovery_geometry_preparation_products = 0
-        self.recovery_geometry_preparation_reduction_adds = 0
-        self.recovery_response_preparation_macs = 0
+        prepared = self.recovery_geometry is not None
+        self.recovery_geometry_bytes = self.recovery_geometry.numel() * 4 if prepared else 0
+        self.recovery_geometry_preparation_products = prepared * 2 * e * i * h
+        self.recovery_geometry_preparation_reduction_adds = prepared * 2 * e * i * (h - 1)
+        self.recovery_response_preparation_macs = prepared * e * i * h * rank
         self.matrix_macs = (
             2 * n * h * (plan.completion_count != n)
             + 2 * plan.completion_count * h
@@ -344,7 +372,9 @@ class ProgressiveReader:
         )
         layer.statistics = statistics.data_ptr()
         layer.norms = self.norms.data_ptr()
-        layer.geometry = None
+        layer.geometry = (
+            self.recovery_geometry.data_ptr() if self.recovery_geometry is not None else None
+        )
         layer.encoder = self.encoder.data_ptr() if self.encoder is not None else None
         layer.decoder = self.decoder.data_ptr() if self.decoder is not None else None
         layer.signs = self.sketch_signs.data_ptr()

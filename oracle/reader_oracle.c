@@ -55,6 +55,9 @@ typedef struct oracle_layer {
   const uint16_t* decoder;    /* bf16 [H, R] or NULL */
   const int8_t* signs;        /* [H] */
   const int32_t* expert_map;  /* [global_experts] or NULL */
+  int32_t score;              /* 0 point, 1 recovery-aware */
+  int32_t reserved;
+  const float* geometry;      /* f32 [E, I, 2] (alpha, beta) or NULL */
 } oracle_layer;
 
 typedef struct oracle_result {
@@ -151,6 +154,32 @@ static float activate(float x, int activation) {
   return x / (1.0f + pinned_exp(-x)); /* SiLU */
 }
 
+/* Recovery-aware score (reference tests/test_progressive_reader.py:146-182,
+ * progressive.py:1304-1353): five-node Gauss-Hermite expectation over the gate. */
+static float risk_score(float g, float u, float vg, float vu, float norm, float alpha, float beta,
+                        float w, int activation) {
+  static const float nodes[5] = {-2.85697007f, -1.35562618f, 0.0f, 1.35562618f, 2.85697007f};
+  static const float mass[5] = {0.0112574113f, 0.222075922f, 0.533333333f, 0.222075922f,
+                                0.0112574113f};
+  const float gb = bf16_round(g), ub = bf16_round(u);
+  const float sg = sqrtf(vg), su = sqrtf(vu);
+  const float spread = (ub * ub) + (su * su);
+  float mu = 0.0f, second = 0.0f;
+  for (int j = 0; j < 5; ++j) {
+    const float a = activate(gb + nodes[j] * sg, activation);
+    mu = mu + (mass[j] * a) * ub;
+    second = second + (mass[j] * (a * a)) * spread;
+  }
+  const float p = bf16_round(activate(gb, activation) * ub);
+  float spread_error = second - mu * mu;
+  if (!(spread_error > 0.0f)) spread_error = 0.0f;
+  float risk = (norm * norm) * spread_error;
+  const float along = norm * mu - alpha * p;
+  const float across = beta * p;
+  risk = risk + ((along * along) + (across * across));
+  return (risk * (w * w)) + 0.0f;
+}
+
 static double activate_f64(double x, int activation) {
   if (activation == 1) {
     return 0.5 * x * (1.0 + tanh(0.7978845608028654 * (x + 0.044715 * x * x * x)));
@@ -193,7 +222,8 @@ static int compare_desc(const void* a, const void* b) {
 /* Rotates one 128-block; writes kept values/coordinates (ascending), their
  * fixed-point copies, the exponent and the sum of the fixed-point values. */
 static void rotate_block(const uint16_t* x, const int8_t* signs, int keep, float* planes,
-                         int32_t* coordinates, int32_t* quantized, int* exponent, int* qsum) {
+                         int32_t* coordinates, int32_t* quantized, int* exponent, int* qsum,
+                         float* energy) {
   float v[BLOCK], next[BLOCK], magnitude[BLOCK], sorted[BLOCK];
   for (int c = 0; c < BLOCK; ++c) v[c] = bf16_to_float(x[c]) * (float)signs[c];
   for (int half = 1; half < BLOCK; half *= 2) {
@@ -224,12 +254,14 @@ static void rotate_block(const uint16_t* x, const int8_t* signs, int keep, float
   if (e > 100) e = 100;
   const float scale = pow2f(QUANT_BITS - e);
   int count = 0, sum = 0;
+  float kept_energy = 0.0f; /* squares of the kept values, in coordinate order */
   for (int c = 0; c < BLOCK; ++c) {
     int member = magnitude[c] > cut;
     if (!member && magnitude[c] == cut && room > 0) {
       member = 1;
       --room;
     }
+    kept_energy = kept_energy + (member ? v[c] * v[c] : 0.0f);
     if (!member) continue;
     long q = top > 0.0f ? lrintf(v[c] * scale) : 0;
     if (q > (1 << 22)) q = 1 << 22;
@@ -242,6 +274,7 @@ static void rotate_block(const uint16_t* x, const int8_t* signs, int keep, float
   }
   *exponent = e;
   *qsum = sum;
+  *energy = kept_energy;
 }
 
 /* ---- selection (reference tests/test_progressive_reader.py:240-246) ---- */
@@ -306,9 +339,11 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
     int32_t* quantized = (int32_t*)malloc(sizeof(int32_t) * B * KEEP);
     int* exponent = (int*)malloc(sizeof(int) * B);
     int* qsum = (int*)malloc(sizeof(int) * B);
+    float* energy = (float*)malloc(sizeof(float) * B);
     for (int b = 0; b < B; ++b)
       rotate_block(x + b * BLOCK, L->signs + b * BLOCK, KEEP, planes + b * KEEP,
-                   coordinates + b * KEEP, quantized + b * KEEP, exponent + b, qsum + b);
+                   coordinates + b * KEEP, quantized + b * KEEP, exponent + b, qsum + b,
+                   energy + b);
     if (out->planes) memcpy(out->planes + (int64_t)t * B * KEEP, planes, sizeof(float) * B * KEEP);
     if (out->coordinates)
       memcpy(out->coordinates + (int64_t)t * B * KEEP, coordinates, sizeof(int32_t) * B * KEEP);
@@ -342,8 +377,21 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
         projection[N + s * I + c] = u;
         const float gb = bf16_round(g), ub = bf16_round(u);
         const float norm = L->norms[(int64_t)e * I + c];
-        const float v = (norm * activate(gb, L->activation)) * ub;
-        score[s * I + c] = ((v * v) * (route[s] * route[s])) + 0.0f;
+        if (L->score == 1) {
+          /* residual variances: sum over blocks, in order, of variance_b * energy_b */
+          float vg = 0.0f, vu = 0.0f;
+          for (int b = 0; b < B; ++b) {
+            const uint16_t* stat = L->statistics + (((int64_t)e * B + b) * 2 + 1) * rows;
+            vg = vg + half_to_float(stat[c]) * energy[b];
+            vu = vu + half_to_float(stat[I + c]) * energy[b];
+          }
+          const float alpha = L->geometry ? L->geometry[((int64_t)e * I + c) * 2] : 0.0f;
+          const float beta = L->geometry ? L->geometry[((int64_t)e * I + c) * 2 + 1] : 0.0f;
+          score[s * I + c] = risk_score(g, u, vg, vu, norm, alpha, beta, route[s], L->activation);
+        } else {
+          const float v = (norm * activate(gb, L->activation)) * ub;
+          score[s * I + c] = ((v * v) * (route[s] * route[s])) + 0.0f;
+        }
       }
     }
     free(trits);
@@ -354,6 +402,7 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
     free(quantized);
     free(exponent);
     free(qsum);
+    free(energy);
   }
   if (out->partial) memcpy(out->partial + (int64_t)t * 2 * N, projection, sizeof(float) * 2 * N);
   if (out->scores) memcpy(out->scores + (int64_t)t * N, score, sizeof(float) * N);

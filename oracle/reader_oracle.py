@@ -41,6 +41,9 @@ class _Layer(ctypes.Structure):
         ("decoder", ctypes.c_void_p),
         ("signs", ctypes.c_void_p),
         ("expert_map", ctypes.c_void_p),
+        ("score", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("geometry", ctypes.c_void_p),
     ]
 
 
@@ -129,6 +132,8 @@ def forward(
     threads: int | None = None,
     given_scores: Tensor | None = None,
     given_selected: Tensor | None = None,
+    score: str = "point",
+    geometry: Tensor | None = None,
 ) -> dict[str, Tensor]:
     """Run the oracle on T tokens.
 
@@ -140,7 +145,8 @@ def forward(
     unrounded FP32 evaluation with `fp32=True`).  `given_scores` `[T, N]` replaces
     the computed scores for the selection (expert parallelism: the sum over
     ranks); `given_selected` `[T, N]` is a kept-channel mask used instead of any
-    selection; `routed` in the result is the FP32 router-weighted sum of the
+    selection; `score` picks the selection score and `geometry` `[E, I, 2]` holds
+    the recovery geometry of the recovery-aware score (zeros if None); `routed` in the result is the FP32 router-weighted sum of the
     local slots before the decoder term.
     """
     lib = load()
@@ -166,6 +172,7 @@ def forward(
     weights32 = _cpu(weights, torch.float32)
     pad = _cpu(padding, torch.uint8) if padding is not None else None
     emap = _cpu(expert_map, torch.int32) if expert_map is not None else None
+    geometry32 = _cpu(geometry, torch.float32) if geometry is not None else None
 
     def pointer(tensor: Tensor | None) -> int | None:
         return tensor.data_ptr() if tensor is not None else None
@@ -176,6 +183,7 @@ def forward(
         pointer(gate_up), pointer(down_rows), pointer(codes), codes.shape[1],
         pointer(stats), pointer(norms), pointer(encoder), pointer(decoder),
         pointer(signs), pointer(emap),
+        {"point": 0, "recovery-aware": 1}[score], 0, pointer(geometry32),
     )
     out = {
         "partial": torch.zeros(tokens, 2, n),

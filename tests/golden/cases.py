@@ -32,6 +32,7 @@ class Case:
     weights: Tensor  # f32 [T, K]
     padding: Tensor | None = None
     activation: str = "silu"
+    score: str = "point"
     notes: dict = field(default_factory=dict)
 
 
@@ -57,7 +58,8 @@ def _synthetic(name: str, config: str, tokens: int, experts: int | None, seed: i
 def _random(name: str, seed: int, h: int, i: int, e: int, k: int, rank: int, tokens: int,
             retention: float, keep: float, activation: str = "silu",
             routes: list[list[int]] | None = None, padding: list[bool] | None = None,
-            zero_input: bool = False, equal_experts: bool = False) -> Case:
+            zero_input: bool = False, equal_experts: bool = False,
+            score: str = "point") -> Case:
     g = torch.Generator().manual_seed(seed)
     gate_up = (torch.randn(e, 2 * i, h, generator=g) / h**0.5).bfloat16()
     down = (torch.randn(e, h, i, generator=g) / i**0.5).bfloat16()
@@ -81,7 +83,7 @@ def _random(name: str, seed: int, h: int, i: int, e: int, k: int, rank: int, tok
         weights = torch.full((tokens, k), 1.0 / k)
     pad = torch.tensor(padding) if padding is not None else None
     return Case(name, _plan(h, i, k, retention, keep), gate_up, down, encoder, decoder,
-                hidden, ids, weights.float(), pad, activation)
+                hidden, ids, weights.float(), pad, activation, score)
 
 
 def build(name: str) -> Case:
@@ -114,6 +116,14 @@ _CASES = {
                                      0.625, equal_experts=True),
     "gemma-gelu": lambda: _random("gemma-gelu", 419, 256, 704, 4, 2, 32, 4, 0.125, 0.625,
                                   "gelu_tanh", routes=[[0, 2], [2, 0], [1, 2], [2, 1]]),
+    # The recovery-aware (Gauss-Hermite) score, with and without a recovery map.
+    "gh-full": lambda: _random("gh-full", 419, 256, 512, 4, 2, 32, 4, 0.2, 1.0,
+                               routes=[[0, 2], [2, 0], [1, 2], [2, 1]], score="recovery-aware"),
+    "gh-keep80-gelu": lambda: _random("gh-keep80-gelu", 503, 256, 704, 4, 2, 32, 2, 0.125, 0.625,
+                                      "gelu_tanh", routes=[[3, 1], [0, 2]],
+                                      score="recovery-aware"),
+    "gh-no-bank": lambda: _random("gh-no-bank", 257, 128, 528, 8, 8, 0, 2, 0.125, 0.625,
+                                  score="recovery-aware"),
 }
 
 NAMES = tuple(_CASES)

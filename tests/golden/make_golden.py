@@ -71,7 +71,23 @@ def main() -> None:
         reader.sketch_codes, reader.sketch_statistics = codes, statistics
         reader.norms = down.float().square().sum(1).sqrt()
         reader.recovery_geometry = None
-        reader.selection_score = "point"
+        if case.score != "point" and case.decoder is not None:
+            # The geometry the reference constructor prepares (progressive.py:3359-3373),
+            # evaluated here on the CPU with the same tensor operations.
+            geometry = torch.zeros(case.gate_up.shape[0], plan.expert_width, 2)
+            decoder_rows = case.decoder.float().T
+            for expert in range(case.gate_up.shape[0]):
+                original = down[expert].float().T
+                response = case.encoder[expert].transpose(0, 1).contiguous().float() @ decoder_rows
+                norm = reader.norms[expert]
+                alpha = (original * response).sum(-1) / torch.where(
+                    norm > 0, norm, torch.ones_like(norm)
+                )
+                beta = (response.square().sum(-1) - alpha.square()).clamp_min(0).sqrt()
+                geometry[expert, :, 0] = alpha
+                geometry[expert, :, 1] = beta
+            reader.recovery_geometry = geometry
+        reader.selection_score = case.score
         reader.activation = case.activation
         reader.selection_threshold = None
         rank = case.decoder.shape[1] if case.decoder is not None else 0

@@ -8,7 +8,7 @@ import numpy as np
 import torch
 
 import cases
-from cfm_b200.reader.progressive import channel_major_down
+from cfm_b200.reader.progressive import channel_major_down, recovery_geometry
 from cfm_b200.reader.sketch import block_hadamard_signs, build_sketch
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
@@ -24,12 +24,20 @@ def prepared(name: str) -> dict:
     case = cases.build(name)
     signs = block_hadamard_signs(case.plan.hidden_size, "cpu")
     codes, statistics = build_sketch(case.gate_up, signs)
+    down = channel_major_down(case.down)
+    geometry = None
+    if case.score != "point" and case.decoder is not None:
+        geometry = recovery_geometry(
+            down, case.encoder.transpose(1, 2).contiguous(), case.decoder,
+            down.float().square().sum(1).sqrt(),
+        )
     return {
         "case": case,
         "signs": signs,
         "codes": codes,
         "statistics": statistics,
-        "down": channel_major_down(case.down),
+        "down": down,
+        "geometry": geometry,
     }
 
 
@@ -39,7 +47,8 @@ def run_oracle(oracle, item: dict, **overrides) -> dict:
         plan=case.plan, gate_up=case.gate_up, down=item["down"], codes=item["codes"],
         statistics=item["statistics"], signs=item["signs"], hidden=case.hidden, ids=case.ids,
         weights=case.weights, encoder=case.encoder, decoder=case.decoder,
-        padding=case.padding, activation=case.activation,
+        padding=case.padding, activation=case.activation, score=case.score,
+        geometry=item.get("geometry"),
     )
     arguments.update(overrides)
     return oracle.forward(**arguments)

@@ -35,7 +35,7 @@ def make_reader(item, capacity=None, **kwargs):
         capacity or case.hidden.shape[0],
         sketch=sketch,
         activation=case.activation,
-        selection_score="point",
+        selection_score=case.score,
         **kwargs,
     )
 
@@ -66,7 +66,10 @@ def test_reader_matches_oracle_and_golden(oracle, name):
     tokens, n, f = case.hidden.shape[0], plan.candidate_count, plan.final_count
     reader = make_reader(item)
     out = run_reader(reader, case).cpu()
-    want = run_oracle(oracle, item, norms=reader.norms.cpu())
+    own = dict(norms=reader.norms.cpu())
+    if reader.recovery_geometry is not None:
+        own["geometry"] = reader.recovery_geometry.cpu()
+    want = run_oracle(oracle, item, **own)
     active = torch.ones(tokens, dtype=torch.bool)
     if case.padding is not None:
         active = ~case.padding
@@ -103,7 +106,7 @@ def test_reader_matches_oracle_and_golden(oracle, name):
     torch.testing.assert_close(
         out.float()[comparable], reference_out[comparable], rtol=0.025, atol=0.02
     )
-    exact = run_oracle(oracle, item, fp32=True, norms=reader.norms.cpu())
+    exact = run_oracle(oracle, item, fp32=True, **own)
     assert relative_l2(out[active], exact["output"][active]) < 1e-2
     if case.padding is not None:
         assert not out[case.padding].any()
@@ -223,6 +226,32 @@ def test_read_counters_follow_the_plan():
         plan.candidate_count - plan.final_count
     )
     assert abs(report["read_fraction"] - 0.1846) < 1e-3
+
+
+def test_recovery_aware_counters_price_residuals_and_geometry():
+    item = prepared("gh-full")
+    case, plan = item["case"], item["case"].plan
+    reader = make_reader(item)
+    assert reader.recovery_geometry is not None and reader.recovery_geometry.shape == (4, 512, 2)
+    run_reader(reader, case)
+    report = reader.report()
+    tokens, rank = 4, reader.rank
+    assert report["physical_sketch_bytes"] == tokens * plan.sketch_read_bytes(residual=True)
+    assert report["selection_parameter_bytes"] == tokens * plan.selection_read_bytes(True)
+    assert report["charged_bytes"] == tokens * (
+        plan.selected_weight_bytes() + plan.sketch_read_bytes(residual=True)
+        + plan.recovery_read_bytes(rank) + plan.selection_read_bytes(True) + plan.hidden_size
+    )
+    # The residual variances the score used: variance plane times the kept energy per block.
+    stats = item["statistics"][..., 1].float()  # [E, 2I, B]
+    energy = reader.norms_input[:tokens].cpu()  # [T, B]
+    ids = reader.ids[:tokens].cpu().long()
+    expected = torch.einsum("tkrb,tb->tkr", stats[ids], energy)  # [T, K, 2I]
+    width = plan.expert_width
+    gate = expected[..., :width].reshape(tokens, -1)
+    up = expected[..., width:].reshape(tokens, -1)
+    torch.testing.assert_close(reader.variances[:tokens, 0].cpu(), gate, rtol=1e-5, atol=1e-7)
+    torch.testing.assert_close(reader.variances[:tokens, 1].cpu(), up, rtol=1e-5, atol=1e-7)
 
 
 def test_contract_violations_raise_before_launch():
