@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 4
+ABI_VERSION = 5
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -61,6 +61,7 @@ class Layer(ctypes.Structure):
         ("signs", ctypes.c_void_p),
         ("expert_map", ctypes.c_void_p),
         ("read_work", ctypes.c_void_p),
+        ("selection_threshold", ctypes.c_void_p),
     ]
 
 

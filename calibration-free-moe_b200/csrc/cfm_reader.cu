@@ -79,6 +79,7 @@ struct Layer {  // device-visible copy of cfm_layer with typed pointers
   const int8_t* signs;
   const int32_t* expert_map;
   double* read_work;
+  const float* threshold;  // device scalar of the threshold mode, or nullptr
 };
 
 // Score of candidate i (slot's channel c of local expert e) of token t; defined with the select kernel.
@@ -205,6 +206,7 @@ static Layer device_layer(const cfm_layer* l) {
   d.signs = l->signs;
   d.expert_map = l->expert_map;
   d.read_work = l->read_work;
+  d.threshold = l->selection_threshold;
   return d;
 }
 
@@ -847,6 +849,16 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     }
     cut = prefix;
     take_ties = remaining;
+    if (L.threshold && !cut_given) {
+      // Threshold mode: every score at or above the layer threshold, at most F
+      // (best first).  When fewer than F reach it, the cut moves up to just below
+      // the threshold's key and no tie budget is needed.
+      const uint32_t floor_key = __float_as_uint(__fadd_rn(*L.threshold, 0.0f));
+      if (cut < floor_key) {
+        cut = floor_key - 1u;
+        take_ties = 0;
+      }
+    }
   }
 
   // Compaction in candidate order: a thread owns a contiguous chunk.  Ties at
@@ -918,7 +930,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     if (k != cut) return k > cut;
     return budgets ? running - s_tie_start[slot] < s_budget[slot] : running < take_ties;
   };
-  int total_kept = F;
+  int total_kept = screened ? (all_counted >> 16) + min(all_counted & 0xffff, take_ties) : F;
   int position = above_before + min(ties_before, take_ties);
   if (!screened) position = begin;
   if (budgets) {
@@ -992,12 +1004,16 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
           screened ? local_slots * L.B * (static_cast<int64_t>(L.KEEP) * (I / 2) + plane) : 0;
       const int64_t selection =
           screened ? ((L.geometry ? 12 : 4) * candidates) : 0;
+      // Threshold mode: every token also reads the FP32 layer threshold (one sector).
+      const int64_t threshold_exact = L.threshold ? 4 : 0, threshold_sector = L.threshold ? 32 : 0;
       int64_t value = 0;
       switch (lane) {
         case 0: case 6: value = native; break;
         case 1: value = reference; break;
         case 3: case 7: value = recovery; break;
-        case 4: case 9: value = selection; break;
+        case 4: value = selection + threshold_exact; break;
+        case 9: value = selection + threshold_sector; break;
+        case 19: value = L.threshold ? 1 : 0; break;
         case 5: value = sketch_exact; break;
         case 10: value = screened ? H : 0; break;
         case 11: value = sketch_issued; break;

@@ -224,8 +224,14 @@ class ProgressiveReader:
         n = plan.candidate_count
         e = gate_up.shape[0] if gate_up.ndim == 3 else -1
         rank = decoder.shape[1] if decoder is not None and decoder.ndim == 2 else 0
-        if selection_threshold is not None:
-            raise ValueError("selection_threshold mode is not provided by this build")
+        if selection_threshold is not None and (
+            not selection_threshold >= 0
+            or selection_threshold == float("inf")
+            or not plan.final_count == plan.completion_count < plan.candidate_count
+        ):
+            raise ValueError(
+                "A selection threshold is finite, nonnegative and needs a screened plan"
+            )
         if selection_score not in SCORE_CODES:
             raise ValueError("selection_score must be 'recovery-aware' or 'point'")
         if activation not in ACTIVATION_CODES:
@@ -258,7 +264,13 @@ class ProgressiveReader:
         self.plan, self.max_tokens, self.rank = plan, max_tokens, rank
         self.activation: GatedActivation = activation
         self.selection_score: SelectionScore = selection_score
-        self.selection_threshold = None
+        # FP32 explicitly (callers may construct readers under a BF16 default dtype); a
+        # device scalar, so it can be refilled between CUDA-graph replays.
+        self.selection_threshold = (
+            torch.tensor([selection_threshold], device=device, dtype=torch.float32)
+            if selection_threshold is not None
+            else None
+        )
         self.expert_map = (
             expert_map.to(device=device, dtype=torch.int32).contiguous()
             if expert_map is not None
@@ -380,6 +392,9 @@ class ProgressiveReader:
         layer.signs = self.sketch_signs.data_ptr()
         layer.expert_map = self.expert_map.data_ptr() if self.expert_map is not None else None
         layer.read_work = self.read_work.data_ptr()
+        layer.selection_threshold = (
+            self.selection_threshold.data_ptr() if self.selection_threshold is not None else None
+        )
         self._layer = layer
         self._library = _native.load()
         self._device = device
@@ -564,7 +579,7 @@ class ProgressiveReader:
             "sketch_bytes": sketch,
             "physical_sketch_bytes": physical_sketch,
             "sketch_resident_bytes": float(self.sketch_resident_bytes),
-            "selection_threshold_resident_bytes": 0.0,
+            "selection_threshold_resident_bytes": 4.0 * (self.selection_threshold is not None),
             "rotation_sign_bytes": rotation_signs,
             "rotation_sign_resident_bytes": float(h),
             "read_fraction": charged / reference if reference else None,
@@ -580,5 +595,23 @@ class ProgressiveReader:
             "matrix_macs_per_token": float(
                 (self.matrix_macs - self.rank * h) / ranks
                 + (self.rank * h if self.recovery_owner else 0)
-            ),
+            )
+            if self.selection_threshold is None
+            else self._threshold_matrix_macs(native, reference, work[19]),
         }
+
+    def _threshold_matrix_macs(self, native: float, reference: float, tokens: float) -> float:
+        """Realised MACs per active token of a thresholded reader (reference :4474-4490).
+
+        Every local slot screens 2 H I; every kept channel (native bytes / 6 H)
+        costs 3 H; recovery encodes the skipped local channels; the owner decodes
+        R x H.
+        """
+        if not tokens:
+            return 0.0
+        p = self.plan
+        h, i = p.hidden_size, p.expert_width
+        slots = reference / (p.native_read_bytes() // p.top_k)
+        kept = native / (6 * h)
+        local = 2 * h * i * slots + 3 * h * kept + self.rank * (i * slots - kept)
+        return local / tokens + (self.rank * h if self.recovery_owner else 0)

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 4
+#define CFM_ABI_VERSION 5
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -70,6 +70,8 @@ typedef struct cfm_layer {
   const int8_t* signs;       /* int8 [H], +-1                                   */
   const int32_t* expert_map; /* i32 [global_experts] global->local, -1 remote   */
   double* read_work;         /* f64 [20] read-cost counters, accumulated        */
+  const float* selection_threshold; /* device f32 scalar: keep scores >= it, at most F
+                                       per token; NULL = plain top-F                 */
 } cfm_layer;
 
 /* One call.  Mirrors the arguments of `ProgressiveReader.__call__`

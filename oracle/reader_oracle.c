@@ -58,6 +58,7 @@ typedef struct oracle_layer {
   int32_t score;              /* 0 point, 1 recovery-aware */
   int32_t reserved;
   const float* geometry;      /* f32 [E, I, 2] (alpha, beta) or NULL */
+  const float* threshold;     /* threshold mode: keep scores >= *threshold, at most F; or NULL */
 } oracle_layer;
 
 typedef struct oracle_result {
@@ -423,8 +424,16 @@ static void token_forward(const oracle_layer* L, int t, const uint16_t* hidden,
       order_by_score[i].index = i;
     }
     qsort(order_by_score, N, sizeof(ranked), compare_ranked);
-    for (int i = 0; i < F; ++i) kept[i] = order_by_score[i].index;
+    int keep_count = F;
+    if (L->threshold) { /* every score at or above the threshold, at most F, best first
+                           (tests/test_progressive_reader.py:229-239) */
+      int passing = 0;
+      for (int i = 0; i < N; ++i) passing += score[i] >= *L->threshold;
+      if (passing < keep_count) keep_count = passing;
+    }
+    for (int i = 0; i < F; ++i) kept[i] = i < keep_count ? order_by_score[i].index : 0x7fffffff;
     qsort(kept, F, sizeof(int32_t), compare_int);
+    for (int i = keep_count; i < F; ++i) kept[i] = -1;
     free(order_by_score);
   } else {
     for (int i = 0; i < F; ++i) kept[i] = i;

@@ -44,6 +44,7 @@ class _Layer(ctypes.Structure):
         ("score", ctypes.c_int32),
         ("reserved", ctypes.c_int32),
         ("geometry", ctypes.c_void_p),
+        ("threshold", ctypes.c_void_p),
     ]
 
 
@@ -134,6 +135,7 @@ def forward(
     given_selected: Tensor | None = None,
     score: str = "point",
     geometry: Tensor | None = None,
+    threshold: float | None = None,
 ) -> dict[str, Tensor]:
     """Run the oracle on T tokens.
 
@@ -146,7 +148,8 @@ def forward(
     the computed scores for the selection (expert parallelism: the sum over
     ranks); `given_selected` `[T, N]` is a kept-channel mask used instead of any
     selection; `score` picks the selection score and `geometry` `[E, I, 2]` holds
-    the recovery geometry of the recovery-aware score (zeros if None); `routed` in the result is the FP32 router-weighted sum of the
+    the recovery geometry of the recovery-aware score (zeros if None); `threshold`
+    switches to the threshold mode (scores at or above it, at most F per token); `routed` in the result is the FP32 router-weighted sum of the
     local slots before the decoder term.
     """
     lib = load()
@@ -173,6 +176,7 @@ def forward(
     pad = _cpu(padding, torch.uint8) if padding is not None else None
     emap = _cpu(expert_map, torch.int32) if expert_map is not None else None
     geometry32 = _cpu(geometry, torch.float32) if geometry is not None else None
+    threshold32 = torch.tensor([threshold], dtype=torch.float32) if threshold is not None else None
 
     def pointer(tensor: Tensor | None) -> int | None:
         return tensor.data_ptr() if tensor is not None else None
@@ -183,7 +187,7 @@ def forward(
         pointer(gate_up), pointer(down_rows), pointer(codes), codes.shape[1],
         pointer(stats), pointer(norms), pointer(encoder), pointer(decoder),
         pointer(signs), pointer(emap),
-        {"point": 0, "recovery-aware": 1}[score], 0, pointer(geometry32),
+        {"point": 0, "recovery-aware": 1}[score], 0, pointer(geometry32), pointer(threshold32),
     )
     out = {
         "partial": torch.zeros(tokens, 2, n),

@@ -33,6 +33,7 @@ class Case:
     padding: Tensor | None = None
     activation: str = "silu"
     score: str = "point"
+    threshold: float | None = None
     notes: dict = field(default_factory=dict)
 
 
@@ -59,7 +60,7 @@ def _random(name: str, seed: int, h: int, i: int, e: int, k: int, rank: int, tok
             retention: float, keep: float, activation: str = "silu",
             routes: list[list[int]] | None = None, padding: list[bool] | None = None,
             zero_input: bool = False, equal_experts: bool = False,
-            score: str = "point") -> Case:
+            score: str = "point", threshold: float | None = None) -> Case:
     g = torch.Generator().manual_seed(seed)
     gate_up = (torch.randn(e, 2 * i, h, generator=g) / h**0.5).bfloat16()
     down = (torch.randn(e, h, i, generator=g) / i**0.5).bfloat16()
@@ -83,7 +84,7 @@ def _random(name: str, seed: int, h: int, i: int, e: int, k: int, rank: int, tok
         weights = torch.full((tokens, k), 1.0 / k)
     pad = torch.tensor(padding) if padding is not None else None
     return Case(name, _plan(h, i, k, retention, keep), gate_up, down, encoder, decoder,
-                hidden, ids, weights.float(), pad, activation, score)
+                hidden, ids, weights.float(), pad, activation, score, threshold)
 
 
 def build(name: str) -> Case:
@@ -124,6 +125,16 @@ _CASES = {
                                       score="recovery-aware"),
     "gh-no-bank": lambda: _random("gh-no-bank", 257, 128, 528, 8, 8, 0, 2, 0.125, 0.625,
                                   score="recovery-aware"),
+    # Threshold mode (reference tests/test_progressive_reader.py:1178-1304): F = N - 1 so the
+    # cap never binds; 0.008925 sits in a wide gap of the scores (kept counts differ per token);
+    # zero keeps the cap; the largest float keeps nothing.
+    "threshold-mid": lambda: _random("threshold-mid", 257, 384, 160, 6, 3, 8, 4, 479 / 480, 0.625,
+                                     threshold=0.008925),
+    "threshold-zero": lambda: _random("threshold-zero", 257, 384, 160, 6, 3, 8, 4, 479 / 480,
+                                      0.625, threshold=0.0),
+    "threshold-max-gh": lambda: _random("threshold-max-gh", 257, 384, 160, 6, 3, 8, 2, 479 / 480,
+                                        1.0, score="recovery-aware",
+                                        threshold=3.4028234663852886e38),
 }
 
 NAMES = tuple(_CASES)

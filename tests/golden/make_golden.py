@@ -89,7 +89,11 @@ def main() -> None:
             reader.recovery_geometry = geometry
         reader.selection_score = case.score
         reader.activation = case.activation
-        reader.selection_threshold = None
+        reader.selection_threshold = (
+            torch.tensor([case.threshold], dtype=torch.float32)
+            if case.threshold is not None
+            else None
+        )
         rank = case.decoder.shape[1] if case.decoder is not None else 0
         e = case.gate_up.shape[0]
         encoder = case.encoder if rank else torch.zeros(e, 1, plan.expert_width)
@@ -103,9 +107,8 @@ def main() -> None:
             "output_bits": output.view(torch.int16).numpy(),
             "selected_ids": np.stack(
                 [
-                    np.pad(row.nonzero().flatten().int().numpy(), (0, plan.final_count))[
-                        : plan.final_count
-                    ]
+                    np.pad(row.nonzero().flatten().int().numpy(), (0, plan.final_count),
+                           constant_values=-1)[: plan.final_count]
                     for row in selected
                 ]
             ),

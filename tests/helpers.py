@@ -48,7 +48,7 @@ def run_oracle(oracle, item: dict, **overrides) -> dict:
         statistics=item["statistics"], signs=item["signs"], hidden=case.hidden, ids=case.ids,
         weights=case.weights, encoder=case.encoder, decoder=case.decoder,
         padding=case.padding, activation=case.activation, score=case.score,
-        geometry=item.get("geometry"),
+        geometry=item.get("geometry"), threshold=case.threshold,
     )
     arguments.update(overrides)
     return oracle.forward(**arguments)

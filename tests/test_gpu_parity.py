@@ -36,6 +36,7 @@ def make_reader(item, capacity=None, **kwargs):
         sketch=sketch,
         activation=case.activation,
         selection_score=case.score,
+        selection_threshold=case.threshold,
         **kwargs,
     )
 
@@ -97,6 +98,10 @@ def test_reader_matches_oracle_and_golden(oracle, name):
         torch.from_numpy(expected["selected_ids"])[comparable],
     )
     counts = want["selected"].reshape(tokens, plan.top_k, -1).sum(-1).int()
+    if case.threshold is not None:
+        assert torch.equal(
+            reader.selected[:tokens].cpu().sum(1)[active], want["selected"].sum(1)[active]
+        )
     assert torch.equal(reader.counts[:tokens].cpu()[active], counts[active])
     starts = counts.cumsum(-1) - counts
     assert torch.equal(reader.starts[:tokens].cpu()[active], starts[active].int())
@@ -252,6 +257,51 @@ def test_recovery_aware_counters_price_residuals_and_geometry():
     up = expected[..., width:].reshape(tokens, -1)
     torch.testing.assert_close(reader.variances[:tokens, 0].cpu(), gate, rtol=1e-5, atol=1e-7)
     torch.testing.assert_close(reader.variances[:tokens, 1].cpu(), up, rtol=1e-5, atol=1e-7)
+
+
+def test_threshold_can_be_refilled_between_graph_replays_and_is_charged(oracle):
+    """Reference tests/test_progressive_reader.py:1178-1304 on this reader."""
+    item = prepared("threshold-mid")
+    case, plan = item["case"], item["case"].plan
+    device = torch.device("cuda:0")
+    reader = make_reader(item)
+    assert reader.selection_threshold.dtype == torch.float32
+    hidden, ids, weights = case.hidden.to(device), case.ids.to(device), case.weights.to(device)
+    out = torch.empty_like(hidden)
+    reader(hidden, ids, weights, None, out)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        reader(hidden, ids, weights, None, out)
+    reader.read_work.zero_()
+    n, h, rank, tokens = plan.candidate_count, plan.hidden_size, reader.rank, 4
+    kept_total = 0
+    for threshold, expected_counts in (
+        (case.threshold, None), (0.0, [n - 1] * tokens), (torch.finfo(torch.float32).max, [0] * tokens),
+    ):
+        reader.selection_threshold.fill_(threshold)
+        graph.replay()
+        torch.cuda.synchronize()
+        want = run_oracle(oracle, item, norms=reader.norms.cpu(), threshold=float(threshold))
+        assert torch.equal(reader.selected[:tokens].cpu(), want["selected"])
+        counts = reader.selected[:tokens].sum(1).tolist()
+        if expected_counts is None:
+            assert len(set(counts)) > 1 and 0 < sum(counts) < tokens * (n - 1)
+        else:
+            assert counts == expected_counts
+        kept_total += sum(counts)
+        torch.testing.assert_close(out.cpu().float(), want["output"], rtol=0.025, atol=0.02)
+    calls = 3 * tokens
+    report = reader.report()
+    assert report["native_expert_coefficient_bytes"] == 6 * h * kept_total
+    assert report["recovery_bytes"] == 2 * rank * (calls * (n + h) - kept_total)
+    assert report["selection_parameter_bytes"] == calls * (4 * n + 4)
+    assert report["physical_selection_parameter_bytes"] == calls * (4 * n + 32)
+    assert report["sketch_bytes"] == calls * plan.sketch_read_bytes(False, False)
+    assert report["selection_threshold_resident_bytes"] == 4
+    k, i = plan.top_k, plan.expert_width
+    macs = k * 2 * h * i + 3 * h * kept_total / calls + rank * (n - kept_total / calls + h)
+    assert report["matrix_macs_per_token"] == pytest.approx(macs)
 
 
 def test_contract_violations_raise_before_launch():
