@@ -177,7 +177,7 @@ class CudaEngine:
         home.scores_ready, home.row_offset = 3, first_row
         with torch.cuda.device(reader.native_gu.device):
             reader._stage("cfm_select", home)
-        return reader.workspace.cuts[: self._rows]
+        return reader.cuts[: self._rows]
 
     def local(self):
         reader, call = self.reader, self._call

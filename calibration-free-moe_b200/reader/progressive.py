@@ -126,11 +126,16 @@ class ReaderWorkspace:
         layout = _native.workspace_layout(_dimension_layer(plan, experts, rank), capacity)
         self.layout = layout
         self.bytes = int(layout.bytes)
+        self.experts, self.rank = experts, rank
         # Zero-initialised: the arrival counters rely on it and reset themselves.
         self.buffer = torch.zeros(self.bytes, dtype=torch.uint8, device=device)
+        self._bind(self, plan, layout)
+
+    def _bind(self, target: object, plan: BudgetPlan, layout: "_native.WorkspaceLayout") -> None:
+        """Attach typed views of the buffer, laid out for `plan`, to `target`."""
         h, i, k = plan.hidden_size, plan.expert_width, plan.top_k
         n, f, keep = plan.candidate_count, plan.final_count, plan.screen_coordinates
-        blocks, c, r = h // 128, capacity, max(rank, 1)
+        blocks, c, r = h // 128, self.capacity, max(self.rank, 1)
         shapes = {
             "ids": (c, k), "weights": (c, k), "norms": (c, blocks),
             "planes": (c, blocks, keep), "coordinates": (c, blocks, keep),
@@ -143,23 +148,41 @@ class ReaderWorkspace:
             "down_parts": (c, layout.down_tiles, h),
             "encoder_parts": (c, k, layout.encoder_tiles, r), "latent": (c, r),
             "status": (4,), "limbs": (c, blocks, 3, 128),
-            "group_offsets": (experts + 1,), "group_pairs": (c * k,), "cuts": (c, k + 1),
+            "group_offsets": (self.experts + 1,), "group_pairs": (c * k,), "cuts": (c, k + 1),
             "variances": (c, 2, n),
         }
         for name, shape in shapes.items():
-            setattr(self, name, self._view(name, shape))
+            setattr(target, name, self._view(layout, name, shape))
         # Reference names for the same arrays.
-        self.sketch_planes, self.sketch_coordinates = self.planes, self.coordinates
-        self.screen_parts = self.parts
-        self.screen_counters = self.counters[: c * k]
-        self.down_splits, self.encoder_splits = layout.down_tiles, layout.encoder_tiles
+        target.sketch_planes, target.sketch_coordinates = target.planes, target.coordinates
+        target.screen_parts = target.parts
+        target.screen_counters = target.counters[: c * k]
+        target.down_splits, target.encoder_splits = layout.down_tiles, layout.encoder_tiles
 
-    def _view(self, name: str, shape: tuple[int, ...]) -> Tensor:
+    def views_for(self, plan: BudgetPlan) -> object:
+        """Views of this buffer laid out for a layer that keeps fewer channels.
+
+        The library lays the workspace out from the dimensions of the layer of each
+        call.  Arrays up to and including the arrival counters do not depend on F,
+        so layers that differ only in F can share one buffer sized for the largest
+        (reference progressive.py:3388-3397); each needs its own views.
+        """
+        layout = _native.workspace_layout(
+            _dimension_layer(plan, self.experts, self.rank), self.capacity
+        )
+        if layout.bytes > self.bytes:
+            raise ValueError("Shared workspace is too small for this plan")
+        views = type("WorkspaceViews", (), {})()
+        views.buffer, views.capacity, views.layout = self.buffer, self.capacity, layout
+        self._bind(views, plan, layout)
+        return views
+
+    def _view(self, layout, name: str, shape: tuple[int, ...]) -> Tensor:
         dtype = _TORCH_TYPES[name]
         count = 1
         for extent in shape:
             count *= extent
-        start = getattr(self.layout, name)
+        start = getattr(layout, name)
         size = count * (1 if dtype is torch.bool else torch.empty((), dtype=dtype).element_size())
         return self.buffer[start : start + size].view(dtype).view(shape)
 
@@ -339,12 +362,23 @@ class ProgressiveReader:
                 plan, e, rank, max_tokens, device, grouped_tokens, grouped_screen_tokens
             )
         workspace_plan = workspace.key[0]
-        if workspace_plan != plan or workspace.key[1:5] != (e, rank, max_tokens, device):
+        compatible_plan = workspace_plan == plan or (
+            workspace_plan.hidden_size == h
+            and workspace_plan.expert_width == i
+            and workspace_plan.top_k == k
+            and workspace_plan.screen_coordinates == plan.screen_coordinates
+            and plan.final_count == plan.completion_count
+            and workspace_plan.final_count == workspace_plan.completion_count
+            and plan.final_count <= workspace_plan.final_count < n
+        )
+        if not compatible_plan or workspace.key[1:5] != (e, rank, max_tokens, device):
             raise ValueError("Shared workspace must match the plan, experts and capacity")
         self.workspace = workspace
-        w = workspace
+        # A layer that keeps fewer channels than the workspace was sized for sees the
+        # shared buffer through views laid out for its own F.
+        w = workspace if workspace_plan == plan else workspace.views_for(plan)
         self.ids, self.weights, self.partial = w.ids, w.weights, w.partial
-        self.variances, self.norms_input = w.variances, w.norms
+        self.variances, self.norms_input, self.cuts = w.variances, w.norms, w.cuts
         self.sketch_planes, self.sketch_coordinates = w.sketch_planes, w.sketch_coordinates
         self.screen_parts, self.screen_counters = w.screen_parts, w.screen_counters
         self.activations, self.completed, self.selected = w.activations, w.completed, w.selected
@@ -355,8 +389,9 @@ class ProgressiveReader:
         self.down_parts, self.encoder_parts, self.latent = (
             w.down_parts, w.encoder_parts, w.latent,
         )
-        self.workspace_bytes = 0 if w.charged else w.bytes
-        w.charged = True
+        # Shared scratch is reported once, by the first reader bound to it.
+        self.workspace_bytes = 0 if workspace.charged else workspace.bytes
+        workspace.charged = True
         prepared = self.recovery_geometry is not None
         self.recovery_geometry_bytes = self.recovery_geometry.numel() * 4 if prepared else 0
         self.recovery_geometry_preparation_products = prepared * 2 * e * i * h

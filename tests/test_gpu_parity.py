@@ -304,6 +304,47 @@ def test_threshold_can_be_refilled_between_graph_replays_and_is_charged(oracle):
     assert report["matrix_macs_per_token"] == pytest.approx(macs)
 
 
+def test_layers_with_different_budgets_share_one_workspace(oracle):
+    """Per-layer budgets (reference progressive.py:3388-3397): one workspace sized for the largest F."""
+    from cfm_b200.reader.budget import compile_budget
+    from cfm_b200.reader.progressive import ReaderWorkspace
+
+    item = prepared("qwen35-e16-t4")
+    case = item["case"]
+    device = torch.device("cuda:0")
+    big = case.plan
+    small = compile_budget(hidden_size=big.hidden_size, expert_width=big.expert_width,
+                           top_k=big.top_k, retention=0.05, screen_keep=0.625)
+    assert small.final_count < big.final_count
+    shared = ReaderWorkspace(big, 16, 64, 4, device)
+    sketch = (item["codes"].to(device), _move_statistics(item["statistics"], device))
+    arguments = (case.gate_up.to(device), _channel_major(item["down"], device),
+                 case.encoder.to(device), case.decoder.to(device))
+    first = ProgressiveReader(*arguments, big, 4, sketch=sketch, workspace=shared,
+                              selection_score="point")
+    second = ProgressiveReader(*arguments, small, 4, sketch=sketch, workspace=shared,
+                               selection_score="point")
+    alone = ProgressiveReader(*arguments, small, 4, sketch=sketch, selection_score="point")
+    assert second.workspace_bytes == 0 and first.workspace_bytes == shared.bytes
+    inputs = (case.hidden.to(device), case.ids.to(device), case.weights.to(device))
+    for _ in range(2):  # interleave the layers on the shared buffer
+        out_big = first(*inputs).clone()
+        out_small = second(*inputs).clone()
+        torch.cuda.synchronize()
+        expected = alone(*inputs)
+        torch.cuda.synchronize()
+        assert torch.equal(out_small, expected)
+        assert torch.equal(second.candidate_ids[-1][:4], alone.candidate_ids[-1][:4])
+        assert second.candidate_ids[-1].shape == (4, small.final_count)
+    want = run_oracle(oracle, item, norms=first.norms.cpu())
+    torch.testing.assert_close(out_big.cpu().float(), want["output"], rtol=0.025, atol=0.02)
+    wrong = compile_budget(hidden_size=big.hidden_size, expert_width=big.expert_width,
+                           top_k=big.top_k, retention=0.3, screen_keep=0.625)
+    with pytest.raises(ValueError):
+        ProgressiveReader(*arguments, wrong, 4, sketch=sketch, workspace=shared,
+                          selection_score="point")
+
+
 def test_contract_violations_raise_before_launch():
     item = prepared("tiny")
     case = item["case"]
