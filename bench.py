@@ -322,6 +322,7 @@ def run_ours(args, shape, plan) -> None:
             readers.append(ProgressiveReader(
                 gate_up, down, encoder, decoder, plan, tokens,
                 selection_score="point", retain_reference_sketch=False,
+                tensor_engine=args.tensor_engine,
             ))
         batches.append(device_batch(shape, router, tokens, g, device))
         del router
@@ -505,6 +506,8 @@ def main() -> None:
     parser.add_argument("--layers", type=int, default=12)
     parser.add_argument("--config", default="qwen3-30b-a3b", choices=sorted(synthetic.CONFIGS))
     parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--tensor-engine", default="mma_sync", choices=("mma_sync", "tcgen05"),
+                        help="tensor-core path of the expert-major screen")
     args = parser.parse_args()
     shape = synthetic.CONFIGS[args.config]
     plan = compile_budget(

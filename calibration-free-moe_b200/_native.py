@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 5
+ABI_VERSION = 6
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -48,7 +48,7 @@ class Layer(ctypes.Structure):
         ("score", ctypes.c_int32),
         ("global_experts", ctypes.c_int32),
         ("recovery_owner", ctypes.c_int32),
-        ("reserved", ctypes.c_int32),
+        ("tensor_engine", ctypes.c_int32),
         ("gate_up", ctypes.c_void_p),
         ("down", ctypes.c_void_p),
         ("sketch", ctypes.c_void_p),

@@ -22,6 +22,7 @@
 #include "cfm_b200.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <mutex>
 
 namespace cfm {
@@ -65,7 +66,7 @@ struct Workspace {
 };
 
 struct Layer {  // device-visible copy of cfm_layer with typed pointers
-  int H, I, E, K, F, KEEP, R, activation, score, global_experts, owner;
+  int H, I, E, K, F, KEEP, R, activation, score, global_experts, owner, tensor_engine;
   int B, N, W;  // blocks, candidates, sketch words per coordinate
   const __nv_bfloat16* gate_up;
   const __nv_bfloat16* down;
@@ -191,6 +192,7 @@ static Layer device_layer(const cfm_layer* l) {
   d.score = l->score;
   d.global_experts = l->global_experts;
   d.owner = l->recovery_owner;
+  d.tensor_engine = l->tensor_engine;
   d.B = d.H / kBlock;
   d.N = d.K * d.I;
   d.W = 2 * d.I / kWordRows;
@@ -684,6 +686,305 @@ __global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Wo
       float* out = ws.partial + static_cast<size_t>(t) * 2 * L.N + static_cast<size_t>(slot) * L.I;
       (row < L.I ? out[row] : out[L.N + row - L.I]) = run[i];
     }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// grouped screen on the 5th-generation tensor cores (tcgen05, TMEM accumulators)
+// ---------------------------------------------------------------------------
+// Same arithmetic as k_screen_grouped (int8 trits x int8 digits -> exact int32
+// block dots), as one M128 x N32 x K32 `tcgen05.mma.kind::i8` per 32 coordinates.
+// A CTA owns 128 sketch rows of one expert and up to ten of its tokens per pass.
+// Per rotation block one ring stage in shared memory holds
+//   A  the 128 rows x 128 coordinates decoded to int8 (K-major canonical layout,
+//      no swizzle: core matrices of 8 rows x 16 bytes, 128 bytes apart along K,
+//      256 bytes apart along M; four K = 32 steps of 4 KiB), and
+//   B  the three int8 digits of the tokens for those 128 coordinates (column
+//      3 token + digit, same layout, four steps of 1 KiB);
+// both written by eight producer warps (a thread decodes 64 coordinates of one
+// row and forwards one 16-byte piece of digits, all fetched one block ahead).
+// One warp issues the MMAs into one of four 32-column int32 accumulators in
+// tensor memory; four epilogue warps read them back (`tcgen05.ld`), rescale per
+// block and keep the running projections in registers.  Stages and
+// accumulators are handed over with mbarriers; every wait is bounded (about a
+// second) and on expiry sets `status[0]`, makes all roles leave, and the CTA
+// still frees its tensor memory.
+namespace tc {
+
+constexpr int kRows = 128;            // sketch rows per CTA (MMA M)
+constexpr int kCols = 32;             // accumulator columns (MMA N)
+constexpr int kTokens = 10;           // tokens per pass: 3 digit columns each
+constexpr int kStages = 4;            // ring stages = accumulators in flight
+constexpr int kStepBytes = kRows * 32;          // one K = 32 step of A
+constexpr int kDigitStepBytes = kCols * 32;     // one K = 32 step of B
+constexpr int kStageBytes = 4 * (kStepBytes + kDigitStepBytes);  // one rotation block
+constexpr int kProducers = 256;                 // eight producer warps
+constexpr int kThreads = 13 * 32;               // 8 producer, 4 epilogue, 1 MMA warp
+constexpr long long kWaitCycles = 2000000000LL;  // bound of every barrier wait
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void barrier_init(uint32_t bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void barrier_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// Waits for the phase with the given parity; false when the wait ran out or
+// another role already gave up.
+__device__ __forceinline__ bool barrier_wait(uint32_t bar, uint32_t parity, volatile int* abort) {
+  const long long start = clock64();
+  for (;;) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (done) return true;
+    if (*abort || clock64() - start > kWaitCycles) {
+      *abort = 1;
+      return false;
+    }
+  }
+}
+
+// Shared-memory matrix descriptor: K-major, no swizzle, 128 bytes between the
+// two 16-byte K chunks of a core-matrix row group, 256 bytes between row groups.
+__device__ __forceinline__ uint64_t matrix_descriptor(uint32_t address) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((address & 0x3ffffu) >> 4);  // start address
+  d |= static_cast<uint64_t>(128 >> 4) << 16;             // leading (K) byte offset
+  d |= static_cast<uint64_t>(256 >> 4) << 32;             // stride (M/N) byte offset
+  d |= static_cast<uint64_t>(1) << 46;                    // descriptor version of sm_100
+  return d;
+}
+
+// Instruction descriptor: int32 accumulate, signed int8 A and B, both K-major.
+__host__ __device__ constexpr uint32_t instruction_descriptor() {
+  return (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kCols >> 3) << 17) |
+         (static_cast<uint32_t>(kRows >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_i8(uint32_t tmem, uint64_t a, uint64_t b, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      :
+      : "r"(tmem), "l"(a), "l"(b), "r"(instruction_descriptor()), "r"(accumulate), "r"(0)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+__host__ __device__ inline size_t shared_bytes(int B) {
+  return static_cast<size_t>(kStages) * kStageBytes + sizeof(float) * kTokens * B + 256;
+}
+
+}  // namespace tc
+
+// grid (ceil(2I / 128), E, passes), 416 threads, dynamic shared memory
+// tc::shared_bytes(B).
+__global__ void __launch_bounds__(tc::kThreads) k_screen_tc(Layer L, Workspace ws) {
+  using namespace tc;
+  extern __shared__ __align__(1024) uint8_t tc_shared[];
+  uint8_t* ring = tc_shared;  // [kStages][A 16 KiB | B 4 KiB]
+  float* unscale = reinterpret_cast<float*>(ring + kStages * kStageBytes);  // [kTokens][B]
+  uint8_t* tail = reinterpret_cast<uint8_t*>(unscale + kTokens * L.B);
+  uint64_t* barriers = reinterpret_cast<uint64_t*>(tail);  // full, empty, ready, freed x stages
+  int* pairs = reinterpret_cast<int*>(tail + 128);         // [kTokens]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tail + 192);
+  volatile int* abort = reinterpret_cast<volatile int*>(tail + 196);
+
+  const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int first = ws.group_offsets[e], total = ws.group_offsets[e + 1] - first;
+  if (total <= static_cast<int>(blockIdx.z) * kTokens) return;  // no pass for this CTA
+  const int rows = 2 * L.I;
+  const uint32_t full = shared_address(barriers), empty = full + 8 * kStages,
+                 ready = empty + 8 * kStages, freed = ready + 8 * kStages;
+
+  if (tid == 0) {
+    *abort = 0;
+    for (int s = 0; s < kStages; ++s) {
+      barrier_init(full + 8 * s, kProducers / 32);  // one lane of every producer warp arrives
+      barrier_init(empty + 8 * s, 1);               // the MMA commit arrives
+      barrier_init(ready + 8 * s, 1);               // the MMA commit arrives
+      barrier_init(freed + 8 * s, 4);               // one lane of every epilogue warp arrives
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 12) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     shared_address(tmem_holder)),
+                 "r"(kStages * kCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = *tmem_holder;
+
+  int iteration = 0;  // rotation blocks processed so far, over all passes
+  for (int base = kTokens * blockIdx.z; base < total; base += kTokens * gridDim.z) {
+    const int count = min(kTokens, total - base);
+    if (tid < kTokens) pairs[tid] = tid < count ? ws.group_pairs[first + base + tid] : -1;
+    __syncthreads();
+    for (int index = tid; index < kTokens * L.B; index += kThreads) {
+      const int token = index / L.B, b = index - token * L.B;
+      const int pair = pairs[token];
+      const int be =
+          pair >= 0 ? ws.exponents[2 * (static_cast<size_t>(pair / L.K) * L.B + b)] : kQuantBits;
+      unscale[index] = __uint_as_float(static_cast<uint32_t>(127 + be - kQuantBits) << 23);
+    }
+    __syncthreads();
+
+    if (warp < 8) {
+      // ---- producers.  Thread (half, local row): coordinates 64 half .. + 63 of
+      // the row (four words, K steps 2 half and 2 half + 1); it also forwards the
+      // 16-byte piece `piece` of digit column `column` of the block.
+      const int half = tid >> 7, local = tid & 127;
+      const int row = blockIdx.x * kRows + local;
+      const bool inside = row < rows;
+      const uint4* source =
+          reinterpret_cast<const uint4*>(L.sketch_grouped +
+                                         (static_cast<size_t>(e) * L.B * rows + (inside ? row : 0)) *
+                                             (kBlock / 16)) + half;
+      const size_t block_stride = static_cast<size_t>(rows) * (kBlock / 16) / 4;  // uint4 per block
+      const int column = tid >> 3, piece = tid & 7;  // 32 columns x 8 pieces
+      const int token = column / 3, digit = column - 3 * token;
+      const int pair = token < kTokens ? pairs[token] : -1;
+      const uint4* digits =
+          pair >= 0 ? reinterpret_cast<const uint4*>(
+                          ws.limbs + (static_cast<size_t>(pair / L.K) * L.B * 3 + digit) * kBlock) + piece
+                    : nullptr;
+      const size_t digit_stride = 3 * kBlock / 16;  // uint4 per block
+      uint8_t* a_dst = ring + (2 * half) * kStepBytes + (local >> 3) * 256 + (local & 7) * 16;
+      uint8_t* b_dst = ring + 4 * kStepBytes + (piece >> 1) * kDigitStepBytes + (column >> 3) * 256 +
+                       (piece & 1) * 128 + (column & 7) * 16;
+      uint4 next_words = inside ? source[0] : make_uint4(0, 0, 0, 0);
+      uint4 next_digits = digits ? digits[0] : make_uint4(0, 0, 0, 0);
+      for (int b = 0; b < L.B && !*abort; ++b) {
+        const int it = iteration + b, stage = it % kStages;
+        const uint4 words = next_words, piece_bytes = next_digits;
+        if (b + 1 < L.B) {
+          if (inside) next_words = source[(b + 1) * block_stride];
+          if (digits) next_digits = digits[(b + 1) * digit_stride];
+        }
+        if (!barrier_wait(empty + 8 * stage, ((it / kStages) & 1) ^ 1, abort)) break;
+        uint8_t* a_out = a_dst + stage * kStageBytes;
+        const uint32_t four[4] = {words.x, words.y, words.z, words.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {  // word w = coordinates 64 half + 16 w .. + 15
+          uint4 bytes;
+          decode_word(four[w], bytes.x, bytes.y, bytes.z, bytes.w);
+          *reinterpret_cast<uint4*>(a_out + (w >> 1) * kStepBytes + (w & 1) * 128) = bytes;
+        }
+        *reinterpret_cast<uint4*>(b_dst + stage * kStageBytes) = piece_bytes;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) barrier_arrive(full + 8 * stage);
+      }
+    } else if (warp == 12) {
+      // ---- MMA issue: one lane; four K = 32 steps per rotation block.
+      if (lane == 0) {
+        for (int b = 0; b < L.B && !*abort; ++b) {
+          const int it = iteration + b, stage = it % kStages;
+          const uint32_t parity = (it / kStages) & 1;
+          if (!barrier_wait(full + 8 * stage, parity, abort)) break;
+          if (!barrier_wait(freed + 8 * stage, parity ^ 1, abort)) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_base = shared_address(ring + stage * kStageBytes);
+          const uint32_t b_base = a_base + 4 * kStepBytes;
+#pragma unroll
+          for (int step = 0; step < 4; ++step)
+            mma_i8(tmem + stage * kCols, matrix_descriptor(a_base + step * kStepBytes),
+                   matrix_descriptor(b_base + step * kDigitStepBytes), step > 0);
+          mma_commit(empty + 8 * stage);  // the stage may be refilled
+          mma_commit(ready + 8 * stage);  // the accumulator may be read
+        }
+      }
+    } else {
+      // ---- epilogue: thread = accumulator lane = sketch row.
+      const int quarter = warp - 8, local = quarter * 32 + lane;
+      const int row = blockIdx.x * kRows + local;
+      const bool inside = row < rows;
+      const __half* scales =
+          L.statistics + static_cast<size_t>(e) * L.B * 2 * rows + (inside ? row : 0);
+      float run[kTokens];
+#pragma unroll
+      for (int t = 0; t < kTokens; ++t) run[t] = 0.0f;
+      float scale = inside ? __half2float(scales[0]) : 0.0f;
+      for (int b = 0; b < L.B && !*abort; ++b) {
+        const int it = iteration + b, stage = it % kStages;
+        const float scale_now = scale;
+        if (inside && b + 1 < L.B)
+          scale = __half2float(scales[static_cast<size_t>(b + 1) * 2 * rows]);
+        if (!barrier_wait(ready + 8 * stage, (it / kStages) & 1, abort)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        uint32_t c[kCols];
+        const uint32_t address = tmem + (static_cast<uint32_t>(quarter * 32) << 16) + stage * kCols;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]), "=r"(c[4]), "=r"(c[5]), "=r"(c[6]),
+              "=r"(c[7]), "=r"(c[8]), "=r"(c[9]), "=r"(c[10]), "=r"(c[11]), "=r"(c[12]),
+              "=r"(c[13]), "=r"(c[14]), "=r"(c[15]), "=r"(c[16]), "=r"(c[17]), "=r"(c[18]),
+              "=r"(c[19]), "=r"(c[20]), "=r"(c[21]), "=r"(c[22]), "=r"(c[23]), "=r"(c[24]),
+              "=r"(c[25]), "=r"(c[26]), "=r"(c[27]), "=r"(c[28]), "=r"(c[29]), "=r"(c[30]),
+              "=r"(c[31])
+            : "r"(address)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) barrier_arrive(freed + 8 * stage);
+#pragma unroll
+        for (int t = 0; t < kTokens; ++t) {
+          if (t < count) {
+            const int dot = static_cast<int>(c[3 * t]) + static_cast<int>(c[3 * t + 1]) * 256 +
+                            static_cast<int>(c[3 * t + 2]) * 65536;
+            const float d = __fmul_rn(__int2float_rn(dot), unscale[t * L.B + b]);
+            run[t] = __fadd_rn(run[t], __fmul_rn(scale_now, d));
+          }
+        }
+      }
+      if (inside && !*abort) {
+#pragma unroll
+        for (int t = 0; t < kTokens; ++t) {
+          if (t < count) {
+            const int pair = pairs[t];
+            const int token = pair / L.K, slot = pair - token * L.K;
+            float* out = ws.partial + static_cast<size_t>(token) * 2 * L.N +
+                         static_cast<size_t>(slot) * L.I;
+            (row < L.I ? out[row] : out[L.N + row - L.I]) = run[t];
+          }
+        }
+      }
+    }
+    iteration += L.B;
+    __syncthreads();
+    if (*abort) break;
+  }
+  if (*abort && tid == 0) atomicExch(&ws.status[0], 1);
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 12) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                 "r"(kStages * kCols)
+                 : "memory");
   }
 }
 
@@ -1590,7 +1891,17 @@ static int run_screen_grouped(const Bound& b) {
   const int64_t per_expert = (static_cast<int64_t>(b.T) * b.L.K + b.L.E - 1) / b.L.E;
   const int passes = static_cast<int>(std::min<int64_t>(8, std::max<int64_t>(1, (per_expert + 7) / 8)));
   const dim3 grid((2 * b.L.I + kGroupRows - 1) / kGroupRows, b.L.E, passes);
-  k_screen_grouped<<<grid, kGroupThreads, 0, b.stream>>>(b.L, b.ws);
+  const size_t tc_bytes = tc::shared_bytes(b.L.B);
+  if (b.L.tensor_engine == CFM_ENGINE_TCGEN05 && tc_bytes <= 200 * 1024) {
+    const cudaError_t err = cudaFuncSetAttribute(
+        k_screen_tc, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(tc_bytes));
+    if (err != cudaSuccess) return static_cast<int>(err);
+    const int tc_passes = static_cast<int>(
+        std::min<int64_t>(8, std::max<int64_t>(1, (per_expert + tc::kTokens - 1) / tc::kTokens)));
+    k_screen_tc<<<dim3(grid.x, grid.y, tc_passes), tc::kThreads, tc_bytes, b.stream>>>(b.L, b.ws);
+  } else {
+    k_screen_grouped<<<grid, kGroupThreads, 0, b.stream>>>(b.L, b.ws);
+  }
   if ((rc = launched())) return rc;
   if (b.padding || b.L.expert_map) {
     k_clear_dead<<<dim3(b.T, (b.L.N + 255) / 256), 256, 0, b.stream>>>(b.L, b.ws, b.padding);

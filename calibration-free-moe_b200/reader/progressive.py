@@ -28,6 +28,7 @@ from .budget import sketch_storage_bytes
 
 SelectionScore = Literal["recovery-aware", "point"]
 SCORE_CODES = {"point": 0, "recovery-aware": 1}
+TENSOR_ENGINES = {"mma_sync": 0, "tcgen05": 1}
 
 # Accepted for interface compatibility; this implementation has one execution
 # path whose results do not depend on them.
@@ -222,6 +223,7 @@ class ProgressiveReader:
         ep_group: "dist.ProcessGroup | None" = None,
         recovery_owner: bool | None = None,
         retain_reference_sketch: bool = True,
+        tensor_engine: str = "mma_sync",
     ) -> None:
         """Prepare the sketch, norms and workspace of one layer.
 
@@ -239,7 +241,9 @@ class ProgressiveReader:
         ranks; defaults to the world group when `expert_map` is given),
         `recovery_owner` (the rank that adds the decoder term; defaults to rank 0
         of the group) and `retain_reference_sketch` (keep the reference-layout
-        codes resident beside the kernel layout).
+        codes resident beside the kernel layout) and `tensor_engine`, the
+        tensor-core path of the expert-major screen: "mma_sync" (default, measured
+        faster) or "tcgen05" (tensor-memory accumulators); both give the same bits.
 
         Contract violations raise ValueError before anything is launched.
         """
@@ -257,6 +261,8 @@ class ProgressiveReader:
             )
         if selection_score not in SCORE_CODES:
             raise ValueError("selection_score must be 'recovery-aware' or 'point'")
+        if tensor_engine not in TENSOR_ENGINES:
+            raise ValueError("tensor_engine must be 'mma_sync' or 'tcgen05'")
         if activation not in ACTIVATION_CODES:
             raise ValueError(f"Unsupported routed expert activation: {activation}")
         if screen_block_splits not in (1, 2, 4, 8) or grouped_screen_splits not in (1, 2, 4, 8):
@@ -409,6 +415,7 @@ class ProgressiveReader:
         layer = _dimension_layer(plan, e, rank)
         layer.activation = ACTIVATION_CODES[activation]
         layer.score = SCORE_CODES[selection_score]
+        layer.tensor_engine = TENSOR_ENGINES[tensor_engine]
         layer.global_experts = self.expert_map.numel() if self.expert_map is not None else 0
         layer.recovery_owner = int(self.recovery_owner)
         layer.gate_up = self.native_gu.data_ptr()

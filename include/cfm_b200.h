@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 5
+#define CFM_ABI_VERSION 6
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -41,6 +41,8 @@ extern "C" {
 #define CFM_ACT_GELU_TANH 1
 #define CFM_SCORE_POINT 0
 #define CFM_SCORE_RECOVERY_AWARE 1
+#define CFM_ENGINE_MMA_SYNC 0 /* warp-level mma.sync.m16n8k32 (default: measured faster) */
+#define CFM_ENGINE_TCGEN05 1  /* tcgen05.mma kind::i8, accumulators in tensor memory     */
 #define CFM_READ_WORK_SLOTS 20
 
 /* One MoE layer: dimensions and resident tensors.  Mirrors the state
@@ -57,7 +59,7 @@ typedef struct cfm_layer {
   int32_t score;          /* CFM_SCORE_*                                       */
   int32_t global_experts; /* length of expert_map, 0 when expert_map is NULL   */
   int32_t recovery_owner; /* 1 if this rank adds the decoder term              */
-  int32_t reserved;
+  int32_t tensor_engine;  /* CFM_ENGINE_*: tensor-core path of the grouped screen */
   const void* gate_up;       /* bf16 [E, 2I, H] contiguous                      */
   const void* down;          /* bf16 physical [E, I, H] (channel-major)         */
   const uint32_t* sketch;    /* coordinate-major layout [E, H, 2I/16], 2 bits per trit */

@@ -143,6 +143,36 @@ def test_results_do_not_depend_on_batch_or_capacity(oracle):
         assert torch.equal(out[0], full[token])
 
 
+@pytest.mark.parametrize("name", ["qwen3-e16-t8", "gh-full"])
+def test_tcgen05_screen_gives_the_same_bits(name):
+    """The tcgen05/TMEM screen against the mma.sync screen and the per-pair screen."""
+    item = prepared(name)
+    case = item["case"]
+    tokens = case.hidden.shape[0]
+    device = torch.device("cuda:0")
+    # Capacity 8 or more switches the screen to the expert-major kernels.
+    legacy = make_reader(item, capacity=max(8, tokens))
+    modern = make_reader(item, capacity=max(8, tokens), tensor_engine="tcgen05")
+    repeat = -(-8 // tokens)
+    hidden = case.hidden.repeat(repeat, 1).to(device)
+    ids = case.ids.repeat(repeat, 1).to(device)
+    weights = case.weights.repeat(repeat, 1).to(device)
+    rows = hidden.shape[0]
+    out_legacy = legacy(hidden, ids, weights).clone()
+    out_modern = modern(hidden, ids, weights).clone()
+    torch.cuda.synchronize()
+    assert int(modern.workspace.status[0]) == 0  # no barrier wait ran out
+    assert torch.equal(modern.partial[:rows], legacy.partial[:rows])
+    assert torch.equal(modern.scores[0][:rows], legacy.scores[0][:rows])
+    assert torch.equal(modern.candidate_ids[-1][:rows], legacy.candidate_ids[-1][:rows])
+    assert torch.equal(out_modern, out_legacy)
+    single = make_reader(item, capacity=1)
+    for row in range(tokens):
+        single(hidden[row : row + 1], ids[row : row + 1], weights[row : row + 1])
+        torch.cuda.synchronize()
+        assert torch.equal(single.partial[0], modern.partial[row])
+
+
 def test_repeated_calls_are_bit_identical():
     item = prepared("qwen35-e16-t4")
     reader = make_reader(item)
