@@ -375,6 +375,40 @@ def test_layers_with_different_budgets_share_one_workspace(oracle):
                           selection_score="point")
 
 
+def test_engine_side_caller_splits_decode_and_prefill_rows():
+    from cfm_b200.runtime.experts import (
+        PhaseContext, ProgressiveExperts, dense_routed_experts, reader_work_report,
+    )
+    from cfm_b200.runtime.ops import register_reader
+
+    item = prepared("qwen35-e16-t4")
+    case = item["case"]
+    device = torch.device("cuda:0")
+    reader = make_reader(item, capacity=2)
+    down = _channel_major(item["down"], device)
+    dense = dense_routed_experts(case.gate_up.to(device), down)
+    experts = ProgressiveExperts(reader, dense, max_policy_rows=2)
+    hidden, ids = case.hidden.to(device), case.ids.to(device).long()
+    weights = case.weights.to(device)
+    # Three decode rows (two reader calls of at most two rows) and one prefill row.
+    out = experts.forward_modular(hidden, weights, ids, PhaseContext(num_decode_tokens=3))
+    torch.cuda.synchronize()
+    direct = make_reader(item, capacity=4)
+    expected = direct(hidden, ids, weights)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:3], expected[:3])
+    torch.testing.assert_close(out[3:].float(), dense(hidden[3:], weights[3:], ids[3:]).float())
+    report = reader_work_report([reader, direct])
+    assert report["reference_bytes"] == 7 * case.plan.native_read_bytes()
+    assert abs(report["read_fraction"] - direct.report()["read_fraction"]) < 1e-12
+    # The same layer through the opaque torch operator.
+    handle = register_reader(direct)
+    again = torch.empty_like(hidden)
+    torch.ops.cfm_b200.reader_forward(hidden, ids, weights, None, again, handle)
+    torch.cuda.synchronize()
+    assert torch.equal(again, expected)
+
+
 def test_contract_violations_raise_before_launch():
     item = prepared("tiny")
     case = item["case"]
