@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 6
+ABI_VERSION = 7
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -87,7 +87,7 @@ _LAYOUT_ARRAYS = (
     "ids", "weights", "norms", "planes", "coordinates", "quantized", "exponents", "parts",
     "counters", "partial", "scores", "selected", "completed", "candidate_ids", "counts",
     "starts", "tile_starts", "activations", "exact", "down_parts", "encoder_parts", "latent",
-    "status", "limbs", "group_offsets", "group_pairs", "cuts", "variances",
+    "status", "limbs", "group_offsets", "group_pairs", "cuts", "variances", "unscales", "zero_limbs",
 )
 
 

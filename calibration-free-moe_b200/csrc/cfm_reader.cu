@@ -59,6 +59,8 @@ struct Workspace {
   int32_t* group_pairs;
   int32_t* cuts;
   float* variances;
+  float* unscales;
+  int8_t* zero_limbs;
   int32_t parts_tokens;
   int32_t down_tiles;
   int32_t encoder_tiles;
@@ -137,6 +139,8 @@ static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layou
   o->group_pairs = take(4 * C * K);
   o->cuts = take(4 * C * (K + 1));
   o->variances = take(4 * C * 2 * N);
+  o->unscales = take(4 * C * B);
+  o->zero_limbs = take(B * 3 * kBlock);
   o->bytes = at;
   return 0;
 }
@@ -172,6 +176,8 @@ static Workspace bind(const cfm_workspace_layout& o, void* base, int32_t capacit
   w.group_pairs = reinterpret_cast<int32_t*>(p + o.group_pairs);
   w.cuts = reinterpret_cast<int32_t*>(p + o.cuts);
   w.variances = reinterpret_cast<float*>(p + o.variances);
+  w.unscales = reinterpret_cast<float*>(p + o.unscales);
+  w.zero_limbs = reinterpret_cast<int8_t*>(p + o.zero_limbs);
   w.parts_tokens = o.parts_tokens;
   w.down_tiles = o.down_tiles;
   w.encoder_tiles = o.encoder_tiles;
@@ -311,6 +317,7 @@ __global__ void __launch_bounds__(kBlock) k_prepare(Layer L, Workspace ws,
     const size_t row = static_cast<size_t>(t) * L.B + b;
     ws.exponents[2 * row] = e;
     ws.exponents[2 * row + 1] = warp_i[0] + warp_i[1] + warp_i[2] + warp_i[3];
+    ws.unscales[row] = __uint_as_float(static_cast<uint32_t>(127 + e - kQuantBits) << 23);
     // Energy of the kept coordinates, summed in coordinate order (pinned).
     float total = 0.0f;
     for (int j = 0; j < kBlock; ++j) total = __fadd_rn(total, sm[j]);
@@ -579,7 +586,7 @@ struct GroupFetch {
   uint2 word_a, word_b;  // 32 coordinates of rows g and g + 8
   uint4 digit[3][2];     // this lane's 32 coordinates of the three digits of token g
   __half scale_a, scale_b;
-  int exponent[2];       // of the two tokens this lane finishes (2 tq, 2 tq + 1)
+  float unscale[2];      // 2^(e - 21) of the two tokens this lane finishes (2 tq, 2 tq + 1)
 };
 
 // grid (ceil(2I / 128), E, passes), 256 threads, no shared memory, no barrier.  A warp
@@ -614,31 +621,37 @@ __global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Wo
     // Pairs of the two tokens whose results this lane finishes.
     const int pair_0 = __shfl_sync(kFull, pair_g, (2 * tq) * 4);
     const int pair_1 = __shfl_sync(kFull, pair_g, (2 * tq + 1) * 4);
-    const int token_g = pair_g >= 0 ? pair_g / L.K : -1;
-    const int token_0 = pair_0 >= 0 ? pair_0 / L.K : -1;
-    const int token_1 = pair_1 >= 0 ? pair_1 / L.K : -1;
-    const int8_t* digits =
-        ws.limbs + static_cast<size_t>(max(token_g, 0)) * L.B * 3 * kBlock + 32 * tq;
-
-    auto fetch = [&](int b) {
+    // Running pointers, advanced by one rotation block per fetch.  Empty token
+    // slots read a block of zero digits kept in the workspace (never written).
+    const uint2* next_a = sketch + sketch_a;
+    const uint2* next_b = sketch + sketch_b;
+    const __half* next_scale_a = scales + row_a;
+    const __half* next_scale_b = scales + row_b;
+    const uint4* next_digits = reinterpret_cast<const uint4*>(
+        (pair_g >= 0 ? ws.limbs + static_cast<size_t>(pair_g / L.K) * L.B * 3 * kBlock
+                     : ws.zero_limbs) + 32 * tq);
+    const float* next_unscale_0 = ws.unscales + static_cast<size_t>(max(pair_0, 0) / L.K) * L.B;
+    const float* next_unscale_1 = ws.unscales + static_cast<size_t>(max(pair_1, 0) / L.K) * L.B;
+    auto fetch = [&]() {
       GroupFetch f;
-      f.word_a = sketch[sketch_a + b * sketch_block];
-      f.word_b = sketch[sketch_b + b * sketch_block];
-      f.scale_a = scales[static_cast<size_t>(b) * 2 * rows + row_a];
-      f.scale_b = scales[static_cast<size_t>(b) * 2 * rows + row_b];
+      f.word_a = *next_a;
+      f.word_b = *next_b;
+      f.scale_a = *next_scale_a;
+      f.scale_b = *next_scale_b;
 #pragma unroll
       for (int j = 0; j < 3; ++j) {
-        f.digit[j][0] = f.digit[j][1] = make_uint4(0, 0, 0, 0);
-        if (token_g >= 0) {
-          const uint4* p = reinterpret_cast<const uint4*>(digits + (b * 3 + j) * kBlock);
-          f.digit[j][0] = p[0];
-          f.digit[j][1] = p[1];
-        }
+        f.digit[j][0] = next_digits[j * (kBlock / 16)];
+        f.digit[j][1] = next_digits[j * (kBlock / 16) + 1];
       }
-      f.exponent[0] = token_0 >= 0 ? ws.exponents[2 * (static_cast<size_t>(token_0) * L.B + b)]
-                                   : kQuantBits;
-      f.exponent[1] = token_1 >= 0 ? ws.exponents[2 * (static_cast<size_t>(token_1) * L.B + b)]
-                                   : kQuantBits;
+      f.unscale[0] = *next_unscale_0;
+      f.unscale[1] = *next_unscale_1;
+      next_a += sketch_block;
+      next_b += sketch_block;
+      next_scale_a += 2 * rows;
+      next_scale_b += 2 * rows;
+      next_digits += 3 * kBlock / 16;
+      ++next_unscale_0;
+      ++next_unscale_1;
       return f;
     };
 
@@ -662,19 +675,17 @@ __global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Wo
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const int dot = acc[0][i] + acc[1][i] * 256 + acc[2][i] * 65536;
-        const float unscale = __uint_as_float(
-            static_cast<uint32_t>(127 + cur.exponent[i & 1] - kQuantBits) << 23);
-        const float d = __fmul_rn(__int2float_rn(dot), unscale);
+        const float d = __fmul_rn(__int2float_rn(dot), cur.unscale[i & 1]);
         run[i] = __fadd_rn(run[i], __fmul_rn(i < 2 ? scale_a : scale_b, d));
       }
     };
     // Two fetch buffers used in turn, so that no block's data is copied between
     // registers: while one block computes the next one's loads are in flight.
-    GroupFetch even = fetch(0), odd;
+    GroupFetch even = fetch(), odd;
     for (int b = 0; b < L.B; b += 2) {
-      if (b + 1 < L.B) odd = fetch(b + 1);
+      if (b + 1 < L.B) odd = fetch();
       compute(even);
-      if (b + 2 < L.B) even = fetch(b + 2);
+      if (b + 2 < L.B) even = fetch();
       if (b + 1 < L.B) compute(odd);
     }
 #pragma unroll

@@ -82,7 +82,7 @@ _TORCH_TYPES = {
     "exact": torch.float32, "down_parts": torch.float32, "encoder_parts": torch.float32,
     "latent": torch.float32, "status": torch.int32, "limbs": torch.int8,
     "group_offsets": torch.int32, "group_pairs": torch.int32, "cuts": torch.int32,
-    "variances": torch.float32,
+    "variances": torch.float32, "unscales": torch.float32, "zero_limbs": torch.int8,
 }
 
 
@@ -150,7 +150,7 @@ class ReaderWorkspace:
             "encoder_parts": (c, k, layout.encoder_tiles, r), "latent": (c, r),
             "status": (4,), "limbs": (c, blocks, 3, 128),
             "group_offsets": (self.experts + 1,), "group_pairs": (c * k,), "cuts": (c, k + 1),
-            "variances": (c, 2, n),
+            "variances": (c, 2, n), "unscales": (c, blocks), "zero_limbs": (blocks, 3, 128),
         }
         for name, shape in shapes.items():
             setattr(target, name, self._view(layout, name, shape))

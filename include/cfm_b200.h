@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 6
+#define CFM_ABI_VERSION 7
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -129,6 +129,8 @@ typedef struct cfm_workspace_layout {
   int64_t group_pairs;    /* i32 [C * K] (token, slot) pairs grouped by expert  */
   int64_t cuts;           /* i32 [C, 1 + K] score cut and per-slot tie budgets   */
   int64_t variances;      /* f32 [C, 2, N] residual variances of the projections */
+  int64_t unscales;       /* f32 [C, B] 2^(exponent - 21), undoes the fixed point */
+  int64_t zero_limbs;     /* i8  [B, 3, 128] zero digits for empty token slots    */
   int32_t parts_tokens;   /* tokens the split screen can serve                  */
   int32_t down_tiles;     /* ceil(F / 128) + K - 1                              */
   int32_t encoder_tiles;  /* ceil(I / 256)                                      */
