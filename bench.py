@@ -144,6 +144,36 @@ def algorithmic_bytes(reader, tokens: int) -> dict[str, float]:
     }
 
 
+def expert_parallel_bytes(sharded, tokens: int, world: int) -> dict[str, float]:
+    """`algorithmic_bytes` of one rank of an expert-parallel layer with a replicated screen.
+
+    The home side screens and encodes this rank's own tokens over all experts; the
+    owner side reads gate, up and down rows of the local experts' kept channels for
+    the tokens of all ranks.
+    """
+    import types
+
+    owner, home = sharded.reader, sharded.home
+    space = home.workspace
+    home_side = algorithmic_bytes(types.SimpleNamespace(
+        plan=owner.plan, rank=home.rank, native_gu=home.norms, ids=space.ids,
+        selected=space.selected, sketch_coordinates=space.sketch_coordinates), tokens)
+    rows = tokens * world
+    kept = torch.zeros(rows, owner.plan.candidate_count + 1, dtype=torch.bool,
+                       device=owner.ids.device)
+    lists = owner.candidate_ids[-1][:rows].long()
+    kept.scatter_(1, torch.where(lists >= 0, lists, owner.plan.candidate_count), True)
+    owner_side = algorithmic_bytes(types.SimpleNamespace(
+        plan=owner.plan, rank=0, native_gu=owner.native_gu, ids=owner.ids,
+        selected=kept[:, :-1].contiguous(), sketch_coordinates=owner.sketch_coordinates), rows)
+    out = {"k_screen": home_side["k_screen"], "k_encode": home_side["k_encode"],
+           "k_output": home_side["k_output"], "k_exact": owner_side["k_exact"],
+           "k_down": owner_side["k_down"]}
+    out["total"] = (home_side["total"] - home_side["k_exact"] - home_side["k_down"]
+                    + owner_side["k_exact"] + owner_side["k_down"])
+    return out
+
+
 class ClockSampler:
     QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -279,8 +309,9 @@ def workload_config(shape, plan, tokens, layers, gpus) -> dict:
         "l2": f"steps cycle over {layers} layers with distinct weights, inputs and workspaces",
         "parallelism": "single GPU" if gpus == 1 else (
             f"expert parallel over {gpus} GPUs: {shape.experts // gpus} experts per rank, "
-            f"{tokens} tokens per rank per step; all_gather dispatch, all_reduce of scores, "
-            "FP32 reduce_scatter combine (NCCL)"),
+            f"{tokens} tokens per rank per step; sketch replicated, home-rank screen and "
+            "selection, all_gather of rows and kept-channel lists, FP32 reduce_scatter "
+            "combine (NCCL)"),
     }
 
 
@@ -427,8 +458,12 @@ def run_ours(args, shape, plan) -> None:
             end.record(stream)
             stream.synchronize()
             stage_ms[name] = begin.elapsed_time(end) / (repeats * layers)
-        bytes_by_kernel = algorithmic_bytes(readers[0], tokens * world)
-        report = readers[0].report()
+        if distributed:
+            bytes_by_kernel = expert_parallel_bytes(sharded[0], tokens, world)
+            report = sharded[0].report()
+        else:
+            bytes_by_kernel = algorithmic_bytes(readers[0], tokens)
+            report = readers[0].report()
 
     times = torch.tensor([elapsed_ms, e2e_ms], device=device, dtype=torch.float64)
     job_bytes = torch.tensor([bytes_by_kernel["total"]], device=device, dtype=torch.float64)
@@ -462,7 +497,9 @@ def run_ours(args, shape, plan) -> None:
             "clocks": clocks,
             "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-            "gpu_launches": (len(STAGES) + (3 if distributed else 1)) * args.steps,
+            # Single GPU: the stages plus the expert grouping.  Expert parallel: six home-side
+            # kernels, four owner-side ones and the finish (NCCL's kernels are not counted).
+            "gpu_launches": (11 if distributed else len(STAGES) + 1) * args.steps,
             "roofline": {
                 "bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak,
                 "unit": "GB/s", "frac": achieved / peak, "traffic": None,

@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 7
+ABI_VERSION = 8
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -28,7 +28,7 @@ NVCC_FLAGS = [
 # Entry points include/cfm_b200.h declares; `load()` checks each one resolves.
 STAGES = (
     "cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_score", "cfm_select", "cfm_exact",
-    "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_reader_forward",
+    "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_adopt", "cfm_reader_forward",
 )
 SYMBOLS = ("cfm_abi_version", "cfm_error_string", "cfm_workspace_layout_for", "cfm_finish") + STAGES
 
@@ -80,6 +80,7 @@ class Call(ctypes.Structure):
         ("weights", ctypes.c_void_p),
         ("padding", ctypes.c_void_p),
         ("out", ctypes.c_void_p),
+        ("lists", ctypes.c_void_p),
     ]
 
 
@@ -167,6 +168,7 @@ def load() -> ctypes.CDLL:
     library.cfm_finish.restype = ctypes.c_int
     library.cfm_finish.argtypes = [
         ctypes.POINTER(Layer), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_void_p,
     ]
     _library = library
     return library

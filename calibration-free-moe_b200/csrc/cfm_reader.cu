@@ -361,6 +361,101 @@ __global__ void __launch_bounds__(32) k_route(Layer L, Workspace ws, const void*
 }
 
 // ---------------------------------------------------------------------------
+// adopt: a selection made on the token's home rank, cut down to this rank's experts
+// ---------------------------------------------------------------------------
+// grid (T), 256 threads.  Expert parallelism with a replicated sketch: the home
+// rank of a token has chosen its kept channels and sent them as a list of
+// candidate ids (slot * I + channel, slots in ascending expert order; ascending,
+// -1 after the last).  This rank orders and maps the router's experts exactly as
+// k_route does, keeps the entries of the slots it owns in their order, and
+// derives the per-slot counts, list starts and down-tile starts for them.
+__global__ void __launch_bounds__(256) k_adopt(Layer L, Workspace ws, const void* ids, int ids64,
+                                               const void* weights, int wbf16,
+                                               const uint8_t* padding, const int32_t* lists) {
+  __shared__ int route[32];
+  __shared__ int count[32];
+  __shared__ int warp_total[8];
+  const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool padded = padding && padding[t];
+  if (warp == 0) {
+    long long id = 0x7fffffffffffffffLL;
+    float w = 0.0f;
+    if (lane < L.K) {
+      const size_t at = static_cast<size_t>(t) * L.K + lane;
+      id = ids64 ? static_cast<const long long*>(ids)[at]
+                 : static_cast<long long>(static_cast<const int32_t*>(ids)[at]);
+      w = wbf16 ? __bfloat162float(static_cast<const __nv_bfloat16*>(weights)[at])
+                : static_cast<const float*>(weights)[at];
+    }
+    int rank = 0;
+    for (int j = 0; j < L.K; ++j) {
+      const long long o = __shfl_sync(kFull, id, j);
+      rank += (o < id) || (o == id && j < lane);
+    }
+    count[lane] = 0;
+    if (lane < L.K) {
+      int local = -1;
+      if (L.expert_map) {
+        if (id >= 0 && id < L.global_experts) local = L.expert_map[id];
+      } else if (id >= 0 && id < L.E) {
+        local = static_cast<int>(id);
+      }
+      if (local >= L.E) local = -1;
+      const size_t out = static_cast<size_t>(t) * L.K + rank;
+      ws.ids[out] = local;
+      ws.weights[out] = w;
+      route[rank] = padded ? -1 : local;
+    }
+  }
+  __syncthreads();
+  const int32_t* in = lists + static_cast<size_t>(t) * L.F;
+  int32_t* out = ws.candidate_ids + static_cast<size_t>(t) * L.F;
+  int kept = 0;
+  for (int base = 0; base < L.F; base += 256) {
+    const int i = base + tid;
+    const int cid = i < L.F ? in[i] : -1;
+    const int slot = cid >= 0 ? min(cid / L.I, L.K - 1) : 0;
+    const bool keep = cid >= 0 && route[slot] >= 0;
+    const unsigned ballot = __ballot_sync(kFull, keep);
+    if (lane == 0) warp_total[warp] = __popc(ballot);
+    __syncthreads();
+    int before = kept, all = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      before += w < warp ? warp_total[w] : 0;
+      all += warp_total[w];
+    }
+    if (keep) {
+      out[before + __popc(ballot & ((1u << lane) - 1))] = cid;
+      atomicAdd(&count[slot], 1);
+    }
+    kept += all;
+    __syncthreads();
+  }
+  for (int i = kept + tid; i < L.F; i += 256) out[i] = -1;
+  if (warp == 0) {
+    const bool live = lane < L.K;
+    const int mine = live ? count[lane] : 0;
+    const int tiles = (mine + kDownTileRows - 1) / kDownTileRows;
+    int rows = mine, scan = tiles;
+#pragma unroll
+    for (int w = 1; w < 32; w <<= 1) {
+      const int r = __shfl_up_sync(kFull, rows, w), o = __shfl_up_sync(kFull, scan, w);
+      if (lane >= w) {
+        rows += r;
+        scan += o;
+      }
+    }
+    if (live) {
+      const size_t pair = static_cast<size_t>(t) * L.K + lane;
+      ws.counts[pair] = mine;
+      ws.starts[pair] = rows - mine;
+      ws.tile_starts[pair] = scan - tiles;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // screen: sketch GEMV + score
 // ---------------------------------------------------------------------------
 // grid (T*K pairs, S splits of the rotation blocks), W*CG threads.  Thread
@@ -1792,15 +1887,17 @@ __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
 }
 
 __global__ void __launch_bounds__(128) k_finish(Layer L, const float* combined,
-                                                __nv_bfloat16* out) {
+                                                const float* latent_rows, __nv_bfloat16* out) {
   __shared__ float latent[256];
   const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
-  const float* row_in = combined + static_cast<size_t>(blockIdx.y) * (L.H + L.R);
+  // The latent rides behind the H sums of a row unless it is given on its own.
+  const float* row_in = combined + static_cast<size_t>(t) * (latent_rows ? L.H : L.H + L.R);
+  const float* latent_in = latent_rows ? latent_rows + static_cast<size_t>(t) * L.R : row_in + L.H;
   const bool recover = L.R > 0 && L.decoder;
   float correction = 0.0f;
   if (recover) {
     for (int r = tid; r < L.R; r += 128)
-      latent[r] = bf16_round(row_in[L.H + r]);
+      latent[r] = bf16_round(latent_in[r]);
     __syncthreads();
     const uint4* row = reinterpret_cast<const uint4*>(L.decoder + static_cast<size_t>(h) * L.R);
     float dot = 0.0f;
@@ -1842,7 +1939,7 @@ static int bind_call(const cfm_layer* layer, void* workspace, int32_t capacity,
   if (rc) return rc;
   if (call->tokens < 1 || call->row_offset < 0 || call->tokens + call->row_offset > capacity)
     return CFM_E_CAPACITY;
-  if (layer->experts < 1 || !layer->gate_up || !layer->down) return CFM_E_NULL;
+  if (layer->experts < 1) return CFM_E_SHAPE;
   if (layer->activation != CFM_ACT_SILU && layer->activation != CFM_ACT_GELU_TANH)
     return CFM_E_UNSUPPORTED;
   if (layer->score != CFM_SCORE_POINT && layer->score != CFM_SCORE_RECOVERY_AWARE)
@@ -1978,7 +2075,7 @@ static int run_score(const Bound& b) {
 }
 
 static int run_exact(const Bound& b, const cfm_call* call) {
-  if (!call->hidden) return CFM_E_NULL;
+  if (!call->hidden || !b.L.gate_up) return CFM_E_NULL;
   const size_t smem = static_cast<size_t>(b.L.H) * 2;
   if (smem > 48 * 1024) {
     const cudaError_t err = cudaFuncSetAttribute(
@@ -1999,6 +2096,7 @@ static int run_exact(const Bound& b, const cfm_call* call) {
 }
 
 static int run_down(const Bound& b) {
+  if (!b.L.down) return CFM_E_NULL;
   k_down<8><<<dim3(b.L.H / 128, b.ws.down_tiles, b.T), 128, 0, b.stream>>>(b.L, b.ws, b.padding);
   return launched();
 }
@@ -2111,8 +2209,8 @@ int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity
   return launched();
 }
 
-int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined, void* out,
-               void* stream) {
+int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined,
+               const float* latent, void* out, void* stream) {
   if (!layer || !combined || !out) return CFM_E_NULL;
   cfm_workspace_layout layout;
   const int rc = make_layout(layer, 1, &layout);  // validates the dimensions
@@ -2120,7 +2218,18 @@ int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined, vo
   if (tokens < 1) return CFM_E_CAPACITY;
   const Layer L = device_layer(layer);
   k_finish<<<dim3(L.H / 128, tokens), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      L, combined, static_cast<__nv_bfloat16*>(out));
+      L, combined, latent, static_cast<__nv_bfloat16*>(out));
+  return launched();
+}
+
+int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const cfm_call* call,
+              void* stream) {
+  Bound b;
+  const int rc = bind_call(layer, workspace, capacity, call, stream, &b);
+  if (rc) return rc;
+  if (!call->ids || !call->weights || !call->lists) return CFM_E_NULL;
+  k_adopt<<<b.T, 256, 0, b.stream>>>(b.L, b.ws, call->ids, call->ids_are_int64, call->weights,
+                                     call->weights_are_bf16, b.padding, call->lists);
   return launched();
 }
 
@@ -2129,6 +2238,7 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
   Bound b;
   int rc = bind_call(layer, workspace, capacity, call, stream, &b);
   if (rc) return rc;
+  if (!layer->gate_up || !layer->down) return CFM_E_NULL;
   if (!call->input_prepared && (rc = run_prepare(b, call))) return rc;
   if ((rc = run_route(b, call))) return rc;
   if ((rc = run_screen(b))) return rc;

@@ -2,19 +2,32 @@
 
 Every rank holds `E / P` consecutive experts (linear placement, as the
 reference's binding requires: runtime/experts.py:677-692) with their gate/up and
-down rows, sketch, norms and encoder rows; the decoder is replicated.  Tokens
-are data parallel: every rank brings its own `T` decode tokens and gets their
-outputs back.
+down rows; the decoder is replicated.  Tokens are data parallel: every rank
+brings its own `T` decode tokens and gets their outputs back.  Two strategies
+share the placement and differ in where the screen runs.
 
-One layer call, on every rank:
+Replicated screen (default).  The sketch, its scales, the down-column norms and
+the recovery encoder of ALL experts are resident on every rank (about a tenth of
+the native weights, gathered once at construction), so the home rank of a token
+screens, selects and encodes it alone, exactly as a single GPU does:
 
-1. dispatch   every rank's tokens, router ids and weights reach the ranks that
-              own their experts (`all_gather` of the hidden rows and of one packed
-              routing record per token; with K = 8 experts over at most 8 ranks
-              nearly every token has an expert on every rank, so the dispatch of
-              a static-shape decode step is the gather of all rows);
+1. choose     the home rank rotates its tokens, screens all K experts of each,
+              selects the kept channels and starts the recovery latent;
+2. dispatch   hidden rows, one packed routing record and the kept candidate ids
+              of every token reach all ranks (three `all_gather`s; the first two
+              do not wait for the selection);
+3. serve      each rank cuts the lists down to the slots whose experts it owns
+              and computes those channels exactly and their down rows;
+4. combine    one FP32 row of router-weighted partial outputs per token goes
+              back to the token's home rank (`reduce_scatter`), which adds the
+              decoder term of its latent and stores BF16.
+
+Sharded screen.  Nothing but the decoder is replicated; ranks screen their own
+experts for all `P * T` tokens and exchange scores:
+
+1. dispatch   hidden rows and routing records reach all ranks (`all_gather`);
 2. screen     each rank scores the candidate channels of its local experts for
-              all `P * T` tokens; slots of remote experts score zero;
+              all tokens; slots of remote experts score zero;
 3. exchange   the per-token top-F is global over the token's K experts: the
               score rows are summed onto each token's home rank
               (`reduce_scatter`), the home rank finds the cut (the F-th largest
@@ -34,13 +47,14 @@ runs once per token instead of once per rank, and the output is reduced in FP32
 before its single BF16 rounding.  The kept channels are the same bit for bit.
 
 The collectives are plain `torch.distributed` calls on tensors, so the same
-orchestration runs over NCCL with the CUDA engine and over gloo with a CPU
-engine in the tests.
+orchestration runs over NCCL with the CUDA engines and over gloo with CPU
+engines in the tests.
 """
 
 from __future__ import annotations
 
 import ctypes
+import types
 from typing import Protocol
 
 import torch
@@ -49,7 +63,7 @@ from torch import Tensor
 
 from .. import _native
 from .budget import BudgetPlan
-from .progressive import ProgressiveReader
+from .progressive import ProgressiveReader, ReaderWorkspace, recovery_geometry
 
 
 def linear_expert_map(global_experts: int, world: int, rank: int) -> Tensor:
@@ -63,7 +77,7 @@ def linear_expert_map(global_experts: int, world: int, rank: int) -> Tensor:
 
 
 class Engine(Protocol):
-    """What the orchestration needs from one rank's compute back end."""
+    """What the sharded-screen orchestration needs from one rank's compute back end."""
 
     def screen(self, hidden: Tensor, ids: Tensor, weights: Tensor, padding: Tensor | None) -> Tensor:
         """Score buffer `[rows, N]`: the local experts' channels scored, zero elsewhere."""
@@ -76,6 +90,20 @@ class Engine(Protocol):
 
     def finish(self, combined: Tensor) -> Tensor:
         """Home-rank output `[T, H]` BF16 from the summed rows."""
+
+
+class HomeEngine(Protocol):
+    """What the replicated-screen orchestration needs from one rank's compute back end."""
+
+    def choose(self, hidden: Tensor, ids: Tensor, weights: Tensor, padding: Tensor | None) -> Tensor:
+        """Kept candidate ids `[T, F]` int32 of this rank's own tokens (ascending, -1 padded)."""
+
+    def serve(self, hidden: Tensor, ids: Tensor, weights: Tensor, padding: Tensor | None,
+              lists: Tensor) -> Tensor:
+        """FP32 rows `[all rows, H]`: router-weighted outputs of the local experts' kept channels."""
+
+    def finish(self, routed: Tensor) -> Tensor:
+        """Home-rank output `[T, H]` BF16 from the summed rows and the latent of `choose`."""
 
 
 def _all_gather_rows(tensor: Tensor, world: int, group) -> Tensor:
@@ -108,6 +136,53 @@ def _reduce_scatter_in_place(buffer: Tensor, world: int, rank: int, group) -> Te
     return mine
 
 
+def _start_gather_rows(tensor: Tensor, world: int, group):
+    """`_all_gather_rows` that returns at once: (gathered tensor, work to wait for)."""
+    out = tensor.new_empty((world * tensor.shape[0], *tensor.shape[1:]))
+    if dist.get_backend(group) == "nccl":
+        work = dist.all_gather_into_tensor(out, tensor.contiguous(), group=group, async_op=True)
+    else:
+        work = dist.all_gather(list(out.chunk(world)), tensor.contiguous(), group=group,
+                               async_op=True)
+    return out, work
+
+
+def _routing_record(ids: Tensor, weights: Tensor, padding: Tensor | None) -> Tensor:
+    """One int32 row per token: expert ids, router weight bits, padding flag."""
+    tokens, k = ids.shape
+    record = torch.empty((tokens, 2 * k + 1), device=ids.device, dtype=torch.int32)
+    record[:, :k] = ids
+    record[:, k : 2 * k] = weights.float().contiguous().view(torch.int32)
+    record[:, 2 * k] = padding.to(torch.int32) if padding is not None else 0
+    return record
+
+
+def replicated_screen_forward(
+    engine: HomeEngine,
+    hidden: Tensor,
+    ids: Tensor,
+    weights: Tensor,
+    padding: Tensor | None = None,
+    group=None,
+) -> Tensor:
+    """One layer call with the screen on the tokens' home ranks (see the module docstring)."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    k = ids.shape[1]
+    # The rows and records travel while the home rank screens and selects.
+    all_hidden, hidden_work = _start_gather_rows(hidden, world, group)
+    all_records, record_work = _start_gather_rows(_routing_record(ids, weights, padding), world, group)
+    lists = engine.choose(hidden, ids, weights, padding)
+    all_lists, list_work = _start_gather_rows(lists, world, group)
+    for work in (hidden_work, record_work, list_work):
+        work.wait()
+    all_ids = all_records[:, :k].contiguous()
+    all_weights = all_records[:, k : 2 * k].contiguous().view(torch.float32)
+    all_padding = all_records[:, 2 * k].bool() if padding is not None else None
+    routed = engine.serve(all_hidden, all_ids, all_weights, all_padding, all_lists)
+    mine = _reduce_scatter_in_place(routed, world, rank, group)
+    return engine.finish(mine)
+
+
 def expert_parallel_forward(
     engine: Engine,
     hidden: Tensor,
@@ -116,16 +191,11 @@ def expert_parallel_forward(
     padding: Tensor | None = None,
     group=None,
 ) -> Tensor:
-    """One layer call under expert parallelism (see the module docstring)."""
+    """One layer call with the screen on the experts' ranks (see the module docstring)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     tokens, k = ids.shape
-    # One routing record per token: ids, weight bits, padding flag, as int32.
-    record = torch.empty((tokens, 2 * k + 1), device=ids.device, dtype=torch.int32)
-    record[:, :k] = ids
-    record[:, k : 2 * k] = weights.float().contiguous().view(torch.int32)
-    record[:, 2 * k] = padding.to(torch.int32) if padding is not None else 0
     all_hidden = _all_gather_rows(hidden, world, group)
-    all_records = _all_gather_rows(record, world, group)
+    all_records = _all_gather_rows(_routing_record(ids, weights, padding), world, group)
     all_ids = all_records[:, :k].contiguous()
     all_weights = all_records[:, k : 2 * k].contiguous().view(torch.float32)
     all_padding = all_records[:, 2 * k].bool() if padding is not None else None
@@ -138,8 +208,8 @@ def expert_parallel_forward(
     return engine.finish(mine)
 
 
-class CudaEngine:
-    """The CUDA library as the compute back end of one rank."""
+class ShardedScreenEngine:
+    """The CUDA library as the sharded-screen back end of one rank."""
 
     def __init__(self, reader: ProgressiveReader) -> None:
         self.reader = reader
@@ -207,8 +277,138 @@ class CudaEngine:
         stream = torch.cuda.current_stream(combined.device).cuda_stream
         with torch.cuda.device(combined.device):
             code = reader._library.cfm_finish(
-                ctypes.byref(reader._layer), rows, combined.data_ptr(), out.data_ptr(),
+                ctypes.byref(reader._layer), rows, combined.data_ptr(), None, out.data_ptr(),
                 ctypes.c_void_p(stream),
+            )
+        _native.check(code, "cfm_finish")
+        return out
+
+
+class _HomeScreen:
+    """Screen, selection and recovery latent of a rank's own tokens over all experts.
+
+    Holds the replicated part of an expert-parallel layer: the sketch (both kernel
+    layouts), its scales, the down-column norms, the transposed recovery encoder
+    and the recovery geometry of every expert, gathered from the ranks that built
+    them for their own experts, and a workspace for this rank's tokens.
+    """
+
+    def __init__(self, owner: ProgressiveReader, encoder: Tensor | None, decoder: Tensor | None,
+                 max_tokens: int, selection_score: str, world: int, group) -> None:
+        plan, device = owner.plan, owner._device
+
+        def gather(local: Tensor | None) -> Tensor | None:
+            return _all_gather_rows(local.contiguous(), world, group) if local is not None else None
+
+        self.sketch_words = gather(owner.sketch_words)
+        self.sketch_grouped_words = gather(owner.sketch_grouped_words)
+        # Physical layout of the statistics is [E, B, 2, 2I].
+        self.sketch_statistics = gather(owner.sketch_statistics.permute(0, 2, 3, 1))
+        self.norms = gather(owner.norms)
+        self.rank = decoder.shape[1] if decoder is not None else 0
+        self.encoder = self.decoder = self.recovery_geometry = None
+        if encoder is not None and decoder is not None:
+            local_encoder = encoder.to(device=device, dtype=torch.bfloat16).transpose(1, 2).contiguous()
+            self.encoder = gather(local_encoder)
+            self.decoder = decoder.to(device=device, dtype=torch.bfloat16).contiguous()
+            if selection_score != "point":
+                self.recovery_geometry = gather(
+                    recovery_geometry(owner.down, local_encoder, self.decoder, owner.norms))
+        experts = self.norms.shape[0]
+        self.workspace = ReaderWorkspace(plan, experts, self.rank, max_tokens, device)
+        self.read_work = torch.zeros(20, device=device, dtype=torch.float64)
+        layer = _native.Layer.from_buffer_copy(owner._layer)
+        layer.experts, layer.rank = experts, self.rank
+        layer.global_experts, layer.recovery_owner = 0, 1
+        layer.gate_up = layer.down = layer.expert_map = None
+        layer.sketch = self.sketch_words.data_ptr()
+        layer.sketch_grouped = (
+            self.sketch_grouped_words.data_ptr() if self.sketch_grouped_words is not None else None)
+        layer.statistics = self.sketch_statistics.data_ptr()
+        layer.norms = self.norms.data_ptr()
+        layer.geometry = (
+            self.recovery_geometry.data_ptr() if self.recovery_geometry is not None else None)
+        layer.encoder = self.encoder.data_ptr() if self.encoder is not None else None
+        layer.decoder = self.decoder.data_ptr() if self.decoder is not None else None
+        layer.read_work = self.read_work.data_ptr()
+        self.layer = layer
+        self.resident_bytes = sum(
+            t.numel() * t.element_size()
+            for t in (self.sketch_words, self.sketch_grouped_words, self.sketch_statistics,
+                      self.norms, self.encoder, self.recovery_geometry) if t is not None)
+
+
+class ReplicatedScreenEngine:
+    """The CUDA library as the replicated-screen back end of one rank."""
+
+    def __init__(self, owner: ProgressiveReader, home: _HomeScreen, max_tokens: int) -> None:
+        self.owner, self.home, self.max_tokens = owner, home, max_tokens
+        device = owner._device
+        self._routed = torch.empty(owner.max_tokens, owner.plan.hidden_size, device=device,
+                                   dtype=torch.float32)
+        # The recovery encoder runs beside the dispatch and the owners' work on its own stream.
+        self._side = torch.cuda.Stream(device, priority=-1)
+        self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+        self._library = owner._library
+
+    def _home_stage(self, name: str, call: _native.Call) -> None:
+        home, device = self.home, self.owner._device
+        code = getattr(self._library, name)(
+            ctypes.byref(home.layer), home.workspace.buffer.data_ptr(), home.workspace.capacity,
+            ctypes.byref(call), ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream),
+        )
+        _native.check(code, name)
+
+    def choose(self, hidden, ids, weights, padding):
+        owner, home, device = self.owner, self.home, self.owner._device
+        rows = hidden.shape[0] if hidden.ndim == 2 else 0
+        if not 1 <= rows <= self.max_tokens:
+            raise ValueError("Sparse input exceeds the prepared token/candidate contract")
+        owner._validate_input(hidden, padding)
+        call = owner._call_struct(rows, hidden, ids, weights, padding, None, False)
+        self._home_keep = (hidden, ids, weights, padding)  # the call struct holds raw pointers
+        plan = owner.plan
+        screened = plan.completion_count < plan.candidate_count
+        with torch.cuda.device(device):
+            if screened:
+                self._home_stage("cfm_prepare_input", call)
+            self._home_stage("cfm_route", call)
+            if screened:
+                self._home_stage("cfm_screen", call)
+            self._home_stage("cfm_select", call)
+            if home.rank:
+                main = torch.cuda.current_stream(device)
+                self._fork.record(main)
+                with torch.cuda.stream(self._side):
+                    self._side.wait_event(self._fork)
+                    self._home_stage("cfm_encode", call)
+                    self._join.record(self._side)
+        self._rows = rows
+        return home.workspace.candidate_ids[:rows]
+
+    def serve(self, hidden, ids, weights, padding, lists):
+        owner = self.owner
+        rows = owner._validate_input(hidden, padding)
+        call = owner._call_struct(rows, hidden, ids, weights, padding, self._routed, False)
+        call.lists = lists.data_ptr()
+        self._serve_keep = (hidden, ids, weights, padding, lists)
+        with torch.cuda.device(owner._device):
+            for stage in ("cfm_adopt", "cfm_exact", "cfm_down", "cfm_partial_output"):
+                owner._stage(stage, call)
+        return self._routed[:rows]
+
+    def finish(self, routed):
+        home, device = self.home, self.owner._device
+        rows = routed.shape[0]
+        out = torch.empty((rows, self.owner.plan.hidden_size), device=device, dtype=torch.bfloat16)
+        with torch.cuda.device(device):
+            main = torch.cuda.current_stream(device)
+            if home.rank:
+                main.wait_event(self._join)
+            code = self._library.cfm_finish(
+                ctypes.byref(home.layer), rows, routed.data_ptr(),
+                home.workspace.latent.data_ptr() if home.rank else None, out.data_ptr(),
+                ctypes.c_void_p(main.cuda_stream),
             )
         _native.check(code, "cfm_finish")
         return out
@@ -222,6 +422,10 @@ class ExpertParallelReader:
     replicated `decoder`, the global expert count, and the group.  `max_tokens`
     is the per-rank batch; every rank must call with the same number of rows
     (use `padding` for ragged batches).  Router ids are global expert ids.
+    `screen` picks the strategy: "replicated" (default; every rank also keeps
+    the sketch, norms and recovery encoder of all experts and screens its own
+    tokens alone) or "sharded" (nothing but the decoder is replicated; ranks
+    exchange scores).  Both keep the same channels.
     """
 
     def __init__(
@@ -235,27 +439,76 @@ class ExpertParallelReader:
         *,
         global_experts: int,
         group=None,
+        screen: str = "replicated",
         **reader_options,
     ) -> None:
+        if screen not in ("replicated", "sharded"):
+            raise ValueError("screen must be 'replicated' or 'sharded'")
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         if gate_up.shape[0] * self.world != global_experts:
             raise ValueError("Local experts times ranks must equal the global expert count")
-        self.max_tokens = max_tokens
+        self.max_tokens, self.screen = max_tokens, screen
         expert_map = linear_expert_map(global_experts, self.world, self.rank)
+        if screen == "sharded":
+            self.reader = ProgressiveReader(
+                gate_up, down, encoder, decoder, plan, self.world * max_tokens,
+                expert_map=expert_map, ep_group=self.group, recovery_owner=True, **reader_options,
+            )
+            self.home = None
+            self.engine = ShardedScreenEngine(self.reader)
+            return
+        if (encoder is None) != (decoder is None):
+            raise ValueError("Expected matching recovery encoder and decoder")
+        # The owner side reads native rows only: no recovery map, no latent.
         self.reader = ProgressiveReader(
-            gate_up, down, encoder, decoder, plan, self.world * max_tokens,
+            gate_up, down, None, None, plan, self.world * max_tokens,
             expert_map=expert_map, ep_group=self.group, recovery_owner=True, **reader_options,
         )
-        self.engine = CudaEngine(self.reader)
+        score = reader_options.get("selection_score", "recovery-aware")
+        self.home = _HomeScreen(self.reader, encoder, decoder, max_tokens, score, self.world,
+                                self.group)
+        # The owner's own sketch now lives inside the gathered copy.
+        local, home = self.reader, self.home
+        span = slice(self.rank * gate_up.shape[0], (self.rank + 1) * gate_up.shape[0])
+        local.sketch_codes = None
+        local.sketch_words = home.sketch_words[span]
+        local._layer.sketch = local.sketch_words.data_ptr()
+        if local.sketch_grouped_words is not None:
+            local.sketch_grouped_words = home.sketch_grouped_words[span]
+            local._layer.sketch_grouped = local.sketch_grouped_words.data_ptr()
+        local.sketch_statistics = home.sketch_statistics[span].permute(0, 3, 1, 2)
+        local._layer.statistics = local.sketch_statistics.data_ptr()
+        local.sketch_resident_bytes = 0
+        self.engine = ReplicatedScreenEngine(self.reader, self.home, max_tokens)
 
     @torch.no_grad()
     def __call__(self, hidden: Tensor, ids: Tensor, weights: Tensor,
                  padding: Tensor | None = None) -> Tensor:
         if hidden.shape[0] > self.max_tokens:
             raise ValueError("Sparse input exceeds the prepared token/candidate contract")
-        return expert_parallel_forward(self.engine, hidden, ids, weights, padding, self.group)
+        forward = replicated_screen_forward if self.home is not None else expert_parallel_forward
+        return forward(self.engine, hidden, ids, weights, padding, self.group)
 
     def report(self) -> dict[str, float | None]:
-        """This rank's read statistics (they add across ranks)."""
-        return self.reader.report()
+        """This rank's read statistics (they add across ranks).
+
+        With the replicated screen a token is accounted whole on its home rank,
+        whichever ranks read its experts' rows.
+        """
+        if self.home is None:
+            return self.reader.report()
+        owner, home = self.reader, self.home
+        plan, rank = owner.plan, home.rank
+        n, h = plan.candidate_count, plan.hidden_size
+        whole = types.SimpleNamespace(
+            read_work=home.read_work, plan=plan, ep_group=None, rank=rank, recovery_owner=True,
+            sketch_resident_bytes=home.resident_bytes,
+            selection_threshold=owner.selection_threshold,
+            workspace_bytes=owner.workspace_bytes + home.workspace.bytes,
+            matrix_macs=(2 * n * h * (plan.completion_count != n) + 2 * plan.completion_count * h
+                         + h * plan.final_count + rank * (n - plan.final_count + h)),
+        )
+        whole._threshold_matrix_macs = types.MethodType(
+            ProgressiveReader._threshold_matrix_macs, whole)
+        return ProgressiveReader.report(whole)

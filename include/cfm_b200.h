@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 7
+#define CFM_ABI_VERSION 8
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -93,6 +93,9 @@ typedef struct cfm_call {
   const void* weights;    /* [T, K] router weights                             */
   const uint8_t* padding; /* bool [T] or NULL; 1 marks a padding row           */
   void* out;              /* bf16 [T, H]                                       */
+  const int32_t* lists;   /* cfm_adopt only: i32 [T, F] kept candidate ids chosen
+                             by the tokens' home ranks, ascending, -1 after the
+                             last; NULL elsewhere                               */
 } cfm_call;
 
 /* Byte offsets of every scratch array inside one workspace allocation of
@@ -218,11 +221,24 @@ int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity
                        const cfm_call* call, void* stream);
 
 /* Expert parallelism, home side: out = bf16(routed + bf16(U bf16(latent))) for
- * `tokens` rows of `combined` f32 [T, H + R], the sums over the ranks of the
- * rows cfm_partial_output wrote.  Needs only hidden, rank and decoder of
- * `layer`.  Replaces: the tail of _output (:2096-2111). */
-int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined, void* out,
-               void* stream);
+ * `tokens` rows.  With `latent` NULL, `combined` is f32 [T, H + R]: the sums
+ * over the ranks of the rows cfm_partial_output wrote.  With `latent` f32
+ * [T, R] (the home rank computed the whole latent itself), `combined` is f32
+ * [T, H].  Needs only hidden, rank and decoder of `layer`.
+ * Replaces: the tail of _output (:2096-2111). */
+int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined,
+               const float* latent, void* out, void* stream);
+
+/* Expert parallelism with the sketch replicated on every rank: the home rank of
+ * a token screens and selects over all K experts and sends the kept candidate
+ * ids; the ranks that own the experts adopt them.  From call->ids, call->weights
+ * (as cfm_route) and call->lists this writes the workspace's routing order, the
+ * list cut down to the local slots, and their counts, starts and down-tile
+ * starts, after which cfm_exact, cfm_down and cfm_partial_output run as usual.
+ * No reference counterpart: the reference replicates the tokens and all-reduces
+ * the scores instead (progressive.py:4245-4251). */
+int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const cfm_call* call,
+              void* stream);
 
 /* The whole layer on one stream: prepare (unless input_prepared), route,
  * screen, select, exact, down, encode, output.  Single-device readers only;

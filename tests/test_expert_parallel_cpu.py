@@ -1,9 +1,10 @@
 """Expert-parallel orchestration on CPU: two gloo ranks, the oracle as the compute engine.
 
 Checks the host logic of `cfm_b200.reader.expert_parallel` (expert placement,
-dispatch, score exchange, combine) without a GPU: every rank holds half of the
-experts and half of the tokens; results must equal the single-process oracle on
-the whole layer (selections exactly, outputs to FP32 re-association).
+dispatch, score or selection exchange, combine) for both strategies without a
+GPU: every rank holds half of the experts and half of the tokens; results must
+equal the single-process oracle on the whole layer (selections exactly, outputs
+to FP32 re-association).
 """
 
 import os
@@ -24,7 +25,7 @@ def _free_port() -> int:
 
 
 class OracleEngine:
-    """CPU stand-in for `CudaEngine`, built on the oracle (test infrastructure)."""
+    """CPU stand-in for `ShardedScreenEngine`, built on the oracle (test infrastructure)."""
 
     def __init__(self, oracle, item, rank, world):
         from cfm_b200.reader.expert_parallel import linear_expert_map
@@ -104,7 +105,58 @@ class OracleEngine:
         return (routed + correction).bfloat16()
 
 
-def _worker(rank, world, port, name, results):
+class OracleHomeEngine:
+    """CPU stand-in for `ReplicatedScreenEngine`, built on the oracle (test infrastructure)."""
+
+    def __init__(self, oracle, item, rank, world):
+        from cfm_b200.reader.expert_parallel import linear_expert_map
+
+        case = item["case"]
+        experts = case.gate_up.shape[0]
+        local = experts // world
+        span = slice(rank * local, (rank + 1) * local)
+        self.oracle, self.case = oracle, case
+        common = dict(plan=case.plan, signs=item["signs"], activation=case.activation, threads=2)
+        # Home side: the sketch and recovery map of every expert (the oracle also takes
+        # the native weights, whose results this side does not use).
+        self.whole = dict(
+            common, gate_up=case.gate_up, down=item["down"], codes=item["codes"],
+            statistics=item["statistics"], encoder=case.encoder, decoder=case.decoder,
+        )
+        # Owner side: native rows of the local experts, no recovery map.
+        self.owned = dict(
+            common, gate_up=case.gate_up[span], down=item["down"][span], codes=item["codes"][span],
+            statistics=item["statistics"][span], encoder=None, decoder=None,
+            expert_map=linear_expert_map(experts, world, rank),
+        )
+        self.selected = None
+
+    def choose(self, hidden, ids, weights, padding):
+        out = self.oracle.forward(**self.whole, hidden=hidden, ids=ids, weights=weights,
+                                  padding=padding)
+        self.latent = out["latent"]
+        return out["candidate_ids"]
+
+    def serve(self, hidden, ids, weights, padding, lists):
+        mask = torch.zeros(hidden.shape[0], self.case.plan.candidate_count, dtype=torch.bool)
+        for row, kept in enumerate(lists):
+            mask[row, kept[kept >= 0].long()] = True
+        out = self.oracle.forward(**self.owned, hidden=hidden, ids=ids, weights=weights,
+                                  padding=padding, given_selected=mask)
+        self.local_ids = out["sorted_ids"]
+        mine = (self.local_ids >= 0).repeat_interleave(self.case.plan.expert_width, dim=1)
+        self.selected = mask & mine
+        return out["routed"]
+
+    def finish(self, routed):
+        correction = 0.0
+        if self.case.decoder is not None:
+            z = self.latent.bfloat16().float()
+            correction = (self.case.decoder.float() @ z.T).T.bfloat16().float()
+        return (routed + correction).bfloat16()
+
+
+def _worker(rank, world, port, name, strategy, results):
     import sys
     from pathlib import Path
 
@@ -113,7 +165,7 @@ def _worker(rank, world, port, name, results):
         if entry not in sys.path:
             sys.path.insert(0, entry)
     import cfm_b200  # noqa: F401
-    from cfm_b200.reader.expert_parallel import expert_parallel_forward
+    from cfm_b200.reader.expert_parallel import expert_parallel_forward, replicated_screen_forward
     from oracle import reader_oracle
 
     torch.set_num_threads(1)
@@ -124,21 +176,25 @@ def _worker(rank, world, port, name, results):
         tokens = case.hidden.shape[0] // world
         rows = slice(rank * tokens, (rank + 1) * tokens)
         padding = case.padding[rows] if case.padding is not None else None
-        engine = OracleEngine(reader_oracle, item, rank, world)
-        out = expert_parallel_forward(
-            engine, case.hidden[rows], case.ids[rows], case.weights[rows], padding
-        )
+        if strategy == "sharded":
+            engine, forward = OracleEngine(reader_oracle, item, rank, world), expert_parallel_forward
+        else:
+            engine = OracleHomeEngine(reader_oracle, item, rank, world)
+            forward = replicated_screen_forward
+        out = forward(engine, case.hidden[rows], case.ids[rows], case.weights[rows], padding)
         results[rank] = (out.float(), engine.selected, engine.local_ids)
     finally:
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("strategy", ["replicated", "sharded"])
 @pytest.mark.parametrize("name", ["tiny", "qwen35-e16-t4", "graph-routes"])
-def test_two_rank_expert_parallel_matches_single_process(oracle, name):
+def test_two_rank_expert_parallel_matches_single_process(oracle, name, strategy):
     world = 2
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(_worker, args=(world, _free_port(), name, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), name, strategy, results), nprocs=world,
+             join=True)
     item = prepared(name)
     case = item["case"]
     want = run_oracle(oracle, item)

@@ -19,11 +19,15 @@ def _free_port() -> int:
         return int(sock.getsockname()[1])
 
 
-def _worker(rank, world, port, name, results):
+def _worker(rank, world, port, name, strategy, results):
+    import faulthandler
     import os
     import sys
     from pathlib import Path
 
+    # A rank stuck in a collective would otherwise block the whole test run: after three
+    # minutes dump where every thread is and leave.
+    faulthandler.dump_traceback_later(180, exit=True)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     root = Path(__file__).resolve().parents[1]
     for entry in (str(root), str(root / "tests"), str(root / "tests" / "golden")):
@@ -57,7 +61,7 @@ def _worker(rank, world, port, name, results):
             case.gate_up[span].to(device), channel_major(item["down"][span]),
             case.encoder[span].to(device) if case.encoder is not None else None,
             case.decoder.to(device) if case.decoder is not None else None,
-            case.plan, tokens, global_experts=experts,
+            case.plan, tokens, global_experts=experts, screen=strategy,
             sketch=(item["codes"][span].to(device), statistics(item["statistics"][span])),
             activation=case.activation, selection_score="point",
         )
@@ -66,9 +70,20 @@ def _worker(rank, world, port, name, results):
                       case.weights[rows].to(device), padding)
         torch.cuda.synchronize()
         total = world * tokens
-        kept = sharded.reader.selected[:total].cpu()
         kept_local = (sharded.reader.ids[:total].cpu() >= 0)
-        scores = sharded.reader.scores[0][rows].cpu()  # summed on the home rank only
+        if strategy == "sharded":
+            kept = sharded.reader.selected[:total].cpu()
+            scores = sharded.reader.scores[0][rows].cpu()  # summed on the home rank only
+        else:
+            # The owner's cut-down lists as a mask; the home rank's scores of its own tokens.
+            kept = torch.zeros(total, case.plan.candidate_count, dtype=torch.bool)
+            for row, ids in enumerate(sharded.reader.candidate_ids[-1][:total].cpu()):
+                kept[row, ids[ids >= 0].long()] = True
+            scores = sharded.home.workspace.scores[:tokens].cpu()
+            home_kept = sharded.home.workspace.candidate_ids[:tokens].cpu()
+            report = sharded.report()
+            if report["reference_bytes"]:  # a rank whose tokens are all padding reads nothing
+                assert 0 < report["read_fraction"] < 1
 
         # Reference-compatible mode: replicated tokens, all-reduce inside the reader.
         replicated = ProgressiveReader(
@@ -102,21 +117,26 @@ def _worker(rank, world, port, name, results):
             torch.cuda.synchronize()
             expected = (reference.float().cpu(), full.candidate_ids[-1][:total].cpu(),
                         full.scores[0][:total].cpu(), full.selected[:total].cpu())
+        if strategy == "replicated" and rank == 0:
+            assert torch.equal(home_kept, expected[1][rows])
         results[rank] = (out.float().cpu(), kept, kept_local, scores, partial.cpu(),
                          compat_kept, expected)
     finally:
         dist.destroy_process_group()
+        faulthandler.cancel_dump_traceback_later()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("strategy", ["replicated", "sharded"])
 @pytest.mark.parametrize("name", ["qwen35-e16-t4", "qwen3-e16-t8", "graph-routes"])
-def test_sharded_reader_matches_single_gpu(name):
+def test_sharded_reader_matches_single_gpu(name, strategy):
     from helpers import prepared
 
     world = 2
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(_worker, args=(world, _free_port(), name, results), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), name, strategy, results), nprocs=world,
+             join=True)
     case = prepared(name)["case"]
     reference, kept, scores, selected = results[0][6]
     tokens = case.hidden.shape[0] // world
@@ -128,7 +148,8 @@ def test_sharded_reader_matches_single_gpu(name):
     for rank in range(world):
         out, rank_kept, rank_local, home_scores, compat, compat_kept, _ = results[rank]
         rows = slice(rank * tokens, (rank + 1) * tokens)
-        # Summed scores of the home tokens equal the single-GPU reader's, bit for bit ...
+        # Scores of the home tokens (summed over the ranks, or computed alone on the
+        # home rank) equal the single-GPU reader's, bit for bit ...
         assert torch.equal(home_scores[active[rows]], scores[rows][active[rows]])
         # ... and every rank keeps, in its own slots, exactly the single-GPU reader's channels.
         mine = rank_local.repeat_interleave(width, dim=1)
