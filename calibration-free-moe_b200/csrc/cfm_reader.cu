@@ -1544,23 +1544,29 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
 // 128 kept rows of one expert over COLS columns with eight 16-byte loads in
 // flight per thread.  GROUPS = 8 (128 columns per CTA) measured fastest at every
 // batch size on B200: it gives the most CTAs and the shortest per-thread chains.
-template <int GROUPS>
+template <int GROUPS, bool STRIDED>
 __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8_t* padding) {
   constexpr int LANES = 128 / GROUPS, COLS = LANES * 8;
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
   __shared__ float red[GROUPS > 1 ? GROUPS : 1][GROUPS > 1 ? COLS : 1];
   __shared__ int s_slot, s_first;
-  const int t = blockIdx.z, tile = blockIdx.y, tid = threadIdx.x;
+  const int t = blockIdx.z, tid = threadIdx.x;
   if (padding && padding[t]) return;
   const size_t token_pairs = static_cast<size_t>(t) * L.K;
+  int used;
   {
     // Tiles are laid out slot after slot; leave at once beyond the last one.
     const size_t last = token_pairs + L.K - 1;
     const int tail =
         ws.ids[last] >= 0 ? (ws.counts[last] + kDownTileRows - 1) / kDownTileRows : 0;
-    if (tile >= ws.tile_starts[last] + tail) return;
+    used = ws.tile_starts[last] + tail;
   }
+  // Under expert parallelism (STRIDED) fewer CTAs than tiles are launched per token,
+  // since a rank owns few of a token's slots; they walk the tiles in strides.
+  int tile = blockIdx.y;
+  if (tile >= used) return;
+  do {
   if (tid == 0) s_slot = -1;
   __syncthreads();
   if (tid < L.K) {  // the slot whose tile range holds this tile, if any
@@ -1575,7 +1581,8 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
   }
   __syncthreads();
   const int slot = s_slot, first = s_first;
-  if (slot < 0) return;
+  if (STRIDED) __syncthreads();  // all have read the slot before the next tile resets it
+  if (slot < 0) continue;  // uniform: every thread read the same slot
   const int e = ws.ids[token_pairs + slot];
   const int rows = min(kDownTileRows, ws.counts[token_pairs + slot] - first);
   const int32_t* list =
@@ -1623,7 +1630,7 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
       out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
       out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
-    return;
+    continue;
   }
   float4* mine = reinterpret_cast<float4*>(&red[GROUPS > 1 ? group : 0][GROUPS > 1 ? lane * 8 : 0]);
   mine[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
@@ -1637,6 +1644,7 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
       parts[blockIdx.x * COLS + c] = sum;
     }
   }
+  } while (STRIDED && (tile += gridDim.y) < used);
 }
 
 // ---------------------------------------------------------------------------
@@ -2097,7 +2105,18 @@ static int run_exact(const Bound& b, const cfm_call* call) {
 
 static int run_down(const Bound& b) {
   if (!b.L.down) return CFM_E_NULL;
-  k_down<8><<<dim3(b.L.H / 128, b.ws.down_tiles, b.T), 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+  int tiles = b.ws.down_tiles;
+  if (b.L.expert_map && b.L.global_experts > 0) {
+    // Expert parallel: about E / global of a token's tiles are local; twice that
+    // share of CTAs is launched per token and walks the tiles in strides.
+    const int64_t share = (2LL * tiles * b.L.E + b.L.global_experts - 1) / b.L.global_experts;
+    tiles = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(tiles, share)));
+  }
+  const dim3 grid(b.L.H / 128, tiles, b.T);
+  if (tiles < b.ws.down_tiles)
+    k_down<8, true><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+  else
+    k_down<8, false><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
   return launched();
 }
 

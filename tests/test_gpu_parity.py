@@ -409,6 +409,61 @@ def test_engine_side_caller_splits_decode_and_prefill_rows():
     assert torch.equal(again, expected)
 
 
+def test_owner_side_adopts_a_home_selection_bit_for_bit():
+    """Expert parallelism with a replicated sketch, owner side, on one GPU.
+
+    The whole layer stands in for a rank that owns 16 of 64 experts and happens
+    to serve every expert of every token: the library then launches fewer CTAs
+    than kept channels and down tiles and walks both in strides.  Adopting the
+    single-GPU reader's kept lists and adding its latent must reproduce its
+    output exactly.
+    """
+    import ctypes
+    import socket
+
+    import torch.distributed as dist
+    from cfm_b200 import _native
+
+    item = prepared("qwen3-e16-t8")
+    case = item["case"]
+    device = torch.device("cuda:0")
+    whole = make_reader(item)
+    expected = run_reader(whole, case)
+    tokens, experts = case.hidden.shape[0], case.gate_up.shape[0]
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        port = sock.getsockname()[1]
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    try:
+        expert_map = torch.full((4 * experts,), -1, dtype=torch.int32)
+        expert_map[:experts] = torch.arange(experts, dtype=torch.int32)
+        owner = ProgressiveReader(
+            case.gate_up.to(device), _channel_major(item["down"], device), None, None,
+            case.plan, tokens, expert_map=expert_map, recovery_owner=True,
+            sketch=(item["codes"].to(device), _move_statistics(item["statistics"], device)),
+            activation=case.activation, selection_score=case.score,
+        )
+    finally:
+        dist.destroy_process_group()
+    hidden, ids, weights = (t.to(device) for t in (case.hidden, case.ids, case.weights))
+    routed = torch.empty(tokens, case.plan.hidden_size, device=device, dtype=torch.float32)
+    call = owner._call_struct(tokens, hidden, ids, weights, None, routed, False)
+    lists = whole.candidate_ids[-1][:tokens].clone()
+    call.lists = lists.data_ptr()
+    for stage in ("cfm_adopt", "cfm_exact", "cfm_down", "cfm_partial_output"):
+        owner._stage(stage, call)
+    out = torch.empty_like(expected)
+    code = whole._library.cfm_finish(
+        ctypes.byref(whole._layer), tokens, routed.data_ptr(), whole.latent.data_ptr(),
+        out.data_ptr(), ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream))
+    _native.check(code, "cfm_finish")
+    torch.cuda.synchronize()
+    assert torch.equal(owner.candidate_ids[-1][:tokens], lists)  # every slot is local
+    assert torch.equal(owner.counts[:tokens], whole.counts[:tokens])
+    assert torch.equal(owner.tile_starts[:tokens], whole.tile_starts[:tokens])
+    assert torch.equal(out, expected)
+
+
 def test_contract_violations_raise_before_launch():
     item = prepared("tiny")
     case = item["case"]
