@@ -99,7 +99,18 @@ def device_batch(shape, router, tokens, generator, device):
 
 
 def algorithmic_bytes(reader, tokens: int) -> dict[str, float]:
+    """`distinct_bytes` of a single-GPU reader's last call."""
+    return distinct_bytes(reader.plan, reader.native_gu.shape[0], reader.rank, reader.ids,
+                          reader.selected, reader.sketch_coordinates, tokens)
+
+
+def distinct_bytes(p, e: int, r: int, ids, selected, coordinates, tokens: int) -> dict[str, float]:
     """Distinct bytes one call must bring from HBM, from the realised routing and selection.
+
+    `p` is the plan, `e` the number of experts the ids index, `r` the recovery rank;
+    `ids` `[T, K]` sorted expert ids (-1 for experts held elsewhere), `selected`
+    `[T, N]` the kept-channel mask, `coordinates` `[T, B, KEEP]` the kept rotated
+    coordinates.
 
     Per routed local expert: the code runs of the union of its tokens' kept
     coordinates (kernel layout, I/2 bytes per coordinate), its FP16 scale planes
@@ -107,12 +118,10 @@ def algorithmic_bytes(reader, tokens: int) -> dict[str, float]:
     rows of the union of skipped channels.  Plus the decoder, the signs and the
     tokens' inputs, outputs and routes.
     """
-    p = reader.plan
-    h, i, k, r = p.hidden_size, p.expert_width, p.top_k, reader.rank
+    h, i, k = p.hidden_size, p.expert_width, p.top_k
     blocks = h // 128
-    e = reader.native_gu.shape[0]
-    ids = reader.ids[:tokens].long()  # [T, K] sorted local ids
-    selected = reader.selected[:tokens].reshape(tokens, k, i)
+    ids = ids[:tokens].long()  # [T, K] sorted local ids
+    selected = selected[:tokens].reshape(tokens, k, i)
     valid = ids >= 0
     flat = ids.clamp_min(0).reshape(-1)
     kept_union = torch.zeros(e, i, dtype=torch.bool, device=ids.device)
@@ -121,7 +130,7 @@ def algorithmic_bytes(reader, tokens: int) -> dict[str, float]:
     skipped_union.index_put_((flat,), ~selected.reshape(-1, i) & valid.reshape(-1, 1), accumulate=True)
     routed = torch.zeros(e, dtype=torch.bool, device=ids.device)
     routed[flat[valid.reshape(-1)]] = True
-    coordinates = reader.sketch_coordinates[:tokens].long()  # [T, B, KEEP]
+    coordinates = coordinates[:tokens].long()  # [T, B, KEEP]
     support = torch.zeros(tokens, blocks, 128, dtype=torch.bool, device=ids.device)
     support.scatter_(-1, coordinates, True)
     support = support.reshape(tokens, h)
@@ -144,6 +153,27 @@ def algorithmic_bytes(reader, tokens: int) -> dict[str, float]:
     }
 
 
+def packed_batch(batch):
+    """The tensors of one step's inputs as views of a single device block.
+
+    The block is attached to the first view as `_packed`; offsets are 256-byte
+    aligned, so the views satisfy the reader's alignment contract.
+    """
+    sizes = [t.numel() * t.element_size() for t in batch]
+    offsets, at = [], 0
+    for size in sizes:
+        offsets.append(at)
+        at = (at + size + 255) // 256 * 256
+    block = torch.empty(at, dtype=torch.uint8, device=batch[0].device)
+    views = []
+    for tensor, offset, size in zip(batch, offsets, sizes):
+        view = block[offset : offset + size].view(tensor.dtype).view(tensor.shape)
+        view.copy_(tensor)
+        views.append(view)
+    views[0]._packed = block
+    return tuple(views)
+
+
 def expert_parallel_bytes(sharded, tokens: int, world: int) -> dict[str, float]:
     """`algorithmic_bytes` of one rank of an expert-parallel layer with a replicated screen.
 
@@ -151,21 +181,17 @@ def expert_parallel_bytes(sharded, tokens: int, world: int) -> dict[str, float]:
     owner side reads gate, up and down rows of the local experts' kept channels for
     the tokens of all ranks.
     """
-    import types
-
     owner, home = sharded.reader, sharded.home
     space = home.workspace
-    home_side = algorithmic_bytes(types.SimpleNamespace(
-        plan=owner.plan, rank=home.rank, native_gu=home.norms, ids=space.ids,
-        selected=space.selected, sketch_coordinates=space.sketch_coordinates), tokens)
+    home_side = distinct_bytes(owner.plan, home.norms.shape[0], home.rank, space.ids,
+                               space.selected, space.sketch_coordinates, tokens)
     rows = tokens * world
     kept = torch.zeros(rows, owner.plan.candidate_count + 1, dtype=torch.bool,
                        device=owner.ids.device)
     lists = owner.candidate_ids[-1][:rows].long()
     kept.scatter_(1, torch.where(lists >= 0, lists, owner.plan.candidate_count), True)
-    owner_side = algorithmic_bytes(types.SimpleNamespace(
-        plan=owner.plan, rank=0, native_gu=owner.native_gu, ids=owner.ids,
-        selected=kept[:, :-1].contiguous(), sketch_coordinates=owner.sketch_coordinates), rows)
+    owner_side = distinct_bytes(owner.plan, owner.native_gu.shape[0], 0, owner.ids,
+                                kept[:, :-1].contiguous(), owner.sketch_coordinates, rows)
     out = {"k_screen": home_side["k_screen"], "k_encode": home_side["k_encode"],
            "k_output": home_side["k_output"], "k_exact": owner_side["k_exact"],
            "k_down": owner_side["k_down"]}
@@ -355,7 +381,7 @@ def run_ours(args, shape, plan) -> None:
                 selection_score="point", retain_reference_sketch=False,
                 tensor_engine=args.tensor_engine,
             ))
-        batches.append(device_batch(shape, router, tokens, g, device))
+        batches.append(packed_batch(device_batch(shape, router, tokens, g, device)))
         del router
     outs = [torch.empty_like(b[0]) for b in batches]
     stream = torch.cuda.Stream(device)
@@ -402,12 +428,13 @@ def run_ours(args, shape, plan) -> None:
         trace("timed region done")
 
         # ---- end to end: host buffers, copies inside the timed region ---
-        host_in = [tuple(t.cpu().pin_memory() for t in b) for b in batches]
+        # A step's inputs (hidden rows, router ids and weights) sit in one block on both
+        # sides, so they cross in one copy.
+        host_in = [(b[0]._packed.cpu().pin_memory(),) for b in batches]
         host_out = [torch.empty_like(o, device="cpu").pin_memory() for o in outs]
 
         def e2e_step(index: int) -> None:
-            for source, target in zip(host_in[index], batches[index]):
-                target.copy_(source, non_blocking=True)
+            batches[index][0]._packed.copy_(host_in[index][0], non_blocking=True)
             graphs[index].replay()
             host_out[index].copy_(outs[index], non_blocking=True)
             stream.synchronize()

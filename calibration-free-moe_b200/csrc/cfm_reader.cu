@@ -1978,10 +1978,21 @@ static int run_prepare(const Bound& b, const cfm_call* call) {
   return launched();
 }
 
+// Batch size from which the screen runs expert-major on the tensor cores.
+constexpr int kGroupedScreenTokens = 8;
+
+static bool screens_grouped(const Bound& b) {
+  return b.L.F < b.L.N && b.L.sketch_grouped && b.T >= kGroupedScreenTokens && b.L.E <= 4096;
+}
+
 static int run_route(const Bound& b, const cfm_call* call) {
   if (!call->ids || !call->weights) return CFM_E_NULL;
   k_route<<<b.T, 32, 0, b.stream>>>(b.L, b.ws, call->ids, call->ids_are_int64, call->weights,
                                     call->weights_are_bf16);
+  int rc = launched();
+  if (rc || !screens_grouped(b)) return rc;
+  // The expert-major screen reads the (token, slot) pairs grouped by expert.
+  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
   return launched();
 }
 
@@ -1999,9 +2010,7 @@ static int launch_screen(const Bound& b, int S) {
 }
 
 static int run_screen_grouped(const Bound& b) {
-  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
-  int rc = launched();
-  if (rc) return rc;
+  int rc = 0;
   // Experts with many tokens (few local experts under expert parallelism) spread
   // their passes of eight tokens over grid.z.
   const int64_t per_expert = (static_cast<int64_t>(b.T) * b.L.K + b.L.E - 1) / b.L.E;
@@ -2026,9 +2035,6 @@ static int run_screen_grouped(const Bound& b) {
   return rc;
 }
 
-// Batch size from which the screen runs expert-major on the tensor cores.
-constexpr int kGroupedScreenTokens = 8;
-
 static int run_screen_projections(const Bound& b);
 
 static int run_screen(const Bound& b) {
@@ -2043,8 +2049,7 @@ static int run_screen(const Bound& b) {
 }
 
 static int run_screen_projections(const Bound& b) {
-  if (b.L.sketch_grouped && b.T >= kGroupedScreenTokens && b.L.E <= 4096)
-    return run_screen_grouped(b);
+  if (screens_grouped(b)) return run_screen_grouped(b);
   // Split the rotation blocks across CTAs while the batch is too small to fill
   // the 148 SMs; large batches keep each pair's blocks in one CTA.
   const int pairs = b.T * b.L.K;
@@ -2258,14 +2263,29 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
   int rc = bind_call(layer, workspace, capacity, call, stream, &b);
   if (rc) return rc;
   if (!layer->gate_up || !layer->down) return CFM_E_NULL;
-  if (!call->input_prepared && (rc = run_prepare(b, call))) return rc;
-  if ((rc = run_route(b, call))) return rc;
+  SideStream side;
+  const bool have_side = b.L.F < b.L.N && side_stream(&side) == 0;
+  if (have_side && !call->input_prepared) {
+    // Routing (and the grouping by expert) does not depend on the rotated input:
+    // it runs on the side stream beside the rotation.
+    cudaError_t err = cudaEventRecord(side.fork, b.stream);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(side.stream, side.fork, 0);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    Bound on_side = b;
+    on_side.stream = side.stream;
+    if ((rc = run_route(on_side, call))) return rc;
+    if ((err = cudaEventRecord(side.join, side.stream)) != cudaSuccess) return static_cast<int>(err);
+    if ((rc = run_prepare(b, call))) return rc;
+    if ((err = cudaStreamWaitEvent(b.stream, side.join, 0)) != cudaSuccess) return static_cast<int>(err);
+  } else {
+    if (!call->input_prepared && (rc = run_prepare(b, call))) return rc;
+    if ((rc = run_route(b, call))) return rc;
+  }
   if ((rc = run_screen(b))) return rc;
   if ((rc = run_select(b, 0))) return rc;
   // The recovery encoder (L2-resident rows, arithmetic) runs beside the two
-  // HBM-bound gathers on a side stream and joins before the output mix.
-  SideStream side;
-  const bool fork = b.L.R > 0 && b.L.F < b.L.N && side_stream(&side) == 0;
+  // HBM-bound gathers on the side stream and joins before the output mix.
+  const bool fork = b.L.R > 0 && have_side;
   if (fork) {
     cudaError_t err = cudaEventRecord(side.fork, b.stream);
     if (err == cudaSuccess) err = cudaStreamWaitEvent(side.stream, side.fork, 0);
