@@ -45,6 +45,17 @@ KERNEL_OF_STAGE = {
 }
 
 
+# DRAM bytes (read + write) per launch from one `ncu --set full` capture of the default
+# workload (profiles/qwen3-30b-a3b_t64_top_kernels_ncu_full.md); a bench run cannot
+# measure them itself.  Reported for that workload only.
+NCU_DRAM_BYTES = {
+    ("qwen3-30b-a3b", 64): {
+        "k_screen": 108.2e6, "k_exact": 344.4e6, "k_down": 158.7e6, "k_encode": 15.8e6,
+        "k_select": 3.6e6, "k_output": 5.8e6, "k_prepare": 0.3e6,
+    },
+}
+
+
 def measured_peaks() -> tuple[float, str]:
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -529,7 +540,9 @@ def run_ours(args, shape, plan) -> None:
             "gpu_launches": (11 if distributed else len(STAGES) + 1) * args.steps,
             "roofline": {
                 "bound": "hbm", "kernel": kernel, "achieved": achieved, "peak": peak,
-                "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_DRAM_BYTES.get((shape.name, tokens), {}).get(kernel)
+                if world == 1 else None,
                 "algorithmic_bytes_per_launch": kernel_bytes,
                 "ms_per_launch": kernel_ms, "peak_source": peak_kind,
             },
