@@ -46,8 +46,8 @@ KERNEL_OF_STAGE = {
 
 
 # DRAM bytes (read + write) per launch from one `ncu --set full` capture of the default
-# workload (profiles/qwen3-30b-a3b_t64_top_kernels_ncu_full.md); a bench run cannot
-# measure them itself.  Reported for that workload only.
+# workload, two layers cycled; a bench run cannot measure them itself.  Reported for that
+# workload only.
 NCU_DRAM_BYTES = {
     ("qwen3-30b-a3b", 64): {
         "k_screen": 108.2e6, "k_exact": 344.4e6, "k_down": 158.7e6, "k_encode": 15.8e6,
