@@ -13,9 +13,9 @@ screens, selects and encodes it alone, exactly as a single GPU does:
 
 1. choose     the home rank rotates its tokens, screens all K experts of each,
               selects the kept channels and starts the recovery latent;
-2. dispatch   hidden rows, one packed routing record and the kept candidate ids
-              of every token reach all ranks (three `all_gather`s; the first two
-              do not wait for the selection);
+2. dispatch   hidden rows, router ids and weights and the kept candidate ids of
+              every token reach all ranks (`all_gather`s; all but the last are
+              started before the screen and do not wait for the selection);
 3. serve      each rank cuts the lists down to the slots whose experts it owns
               and computes those channels exactly and their down rows;
 4. combine    one FP32 row of router-weighted partial outputs per token goes
@@ -167,17 +167,19 @@ def replicated_screen_forward(
 ) -> Tensor:
     """One layer call with the screen on the tokens' home ranks (see the module docstring)."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
-    k = ids.shape[1]
-    # The rows and records travel while the home rank screens and selects.
-    all_hidden, hidden_work = _start_gather_rows(hidden, world, group)
-    all_records, record_work = _start_gather_rows(_routing_record(ids, weights, padding), world, group)
+    # Rows and router outputs travel while the home rank screens and selects; they are
+    # gathered as they are, so nothing has to be packed before or sliced after.
+    pending = [_start_gather_rows(hidden, world, group), _start_gather_rows(ids, world, group),
+               _start_gather_rows(weights, world, group)]
+    if padding is not None:
+        pending.append(_start_gather_rows(padding.view(torch.uint8), world, group))
     lists = engine.choose(hidden, ids, weights, padding)
-    all_lists, list_work = _start_gather_rows(lists, world, group)
-    for work in (hidden_work, record_work, list_work):
+    pending.append(_start_gather_rows(lists, world, group))
+    for _, work in pending:
         work.wait()
-    all_ids = all_records[:, :k].contiguous()
-    all_weights = all_records[:, k : 2 * k].contiguous().view(torch.float32)
-    all_padding = all_records[:, 2 * k].bool() if padding is not None else None
+    all_hidden, all_ids, all_weights = (gathered for gathered, _ in pending[:3])
+    all_padding = pending[3][0].view(torch.bool) if padding is not None else None
+    all_lists = pending[-1][0]
     routed = engine.serve(all_hidden, all_ids, all_weights, all_padding, all_lists)
     mine = _reduce_scatter_in_place(routed, world, rank, group)
     return engine.finish(mine)
