@@ -409,14 +409,15 @@ def test_engine_side_caller_splits_decode_and_prefill_rows():
     assert torch.equal(again, expected)
 
 
-def test_owner_side_adopts_a_home_selection_bit_for_bit():
+@pytest.mark.parametrize("name", ["qwen3-e16-t8", "dense-bypass", "gemma-gelu"])
+def test_owner_side_adopts_a_home_selection_bit_for_bit(name):
     """Expert parallelism with a replicated sketch, owner side, on one GPU.
 
-    The whole layer stands in for a rank that owns 16 of 64 experts and happens
-    to serve every expert of every token: the library then launches fewer CTAs
-    than kept channels and down tiles and walks both in strides.  Adopting the
-    single-GPU reader's kept lists and adding its latent must reproduce its
-    output exactly.
+    The whole layer stands in for a rank that owns a quarter of the experts and
+    happens to serve every expert of every token: the library then launches
+    fewer CTAs than kept channels and down tiles and walks both in strides.
+    Adopting the single-GPU reader's kept lists and adding its latent must
+    reproduce its output exactly (also for an unscreened plan, F = N).
     """
     import ctypes
     import socket
@@ -424,7 +425,7 @@ def test_owner_side_adopts_a_home_selection_bit_for_bit():
     import torch.distributed as dist
     from cfm_b200 import _native
 
-    item = prepared("qwen3-e16-t8")
+    item = prepared(name)
     case = item["case"]
     device = torch.device("cuda:0")
     whole = make_reader(item)
