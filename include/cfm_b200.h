@@ -160,18 +160,22 @@ int cfm_prepare_input(const cfm_layer* layer, void* workspace, int32_t capacity,
                       const cfm_call* call, void* stream);
 
 /* Route: per token, sort the K expert ids ascending (stable), carry the
- * weights, map global to local ids.  Replaces: _prepare / _route
- * (progressive.py:143-239,349-386). */
+ * weights, map global to local ids; for batches the screen runs expert-major
+ * (8 tokens and more, row-major sketch present) also group the (token, slot)
+ * pairs by expert.  Independent of cfm_prepare_input: the two may run on
+ * different streams.  Replaces: _prepare / _route (progressive.py:143-239,
+ * 349-386), _group_sort (:2329-2382). */
 int cfm_route(const cfm_layer* layer, void* workspace, int32_t capacity,
               const cfm_call* call, void* stream);
 
 /* Screen: sketch projections of every candidate channel of every routed local
  * expert.  Writes `partial`; rows of remote or padded slots are zero.  Small
  * batches run one GEMV per (token, expert) over the coordinate-major sketch;
- * from 8 tokens the pairs are grouped by expert and run on the tensor cores
- * over the row-major sketch (when the layer has one).  Both give the same bits.
+ * from 8 tokens the pairs, grouped by expert by cfm_route, run on the tensor
+ * cores over the row-major sketch (when the layer has one).  Both give the same
+ * bits.  Needs cfm_prepare_input and cfm_route of the same rows.
  * Replaces: _sketch_screen and its helpers (progressive.py:478-1066),
- * _group_sort (:2329-2382), _group_screen (:2428-2606). */
+ * _group_screen (:2428-2606). */
 int cfm_screen(const cfm_layer* layer, void* workspace, int32_t capacity,
                const cfm_call* call, void* stream);
 
