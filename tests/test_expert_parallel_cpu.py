@@ -1,4 +1,4 @@
-"""Expert-parallel orchestration on CPU: two gloo ranks, the oracle as the compute engine.
+"""Expert-parallel orchestration on CPU: two and four gloo ranks, the oracle as the compute engine.
 
 Checks the host logic of `cfm_b200.reader.expert_parallel` (expert placement,
 dispatch, score or selection exchange, combine) for both strategies without a
@@ -187,10 +187,13 @@ def _worker(rank, world, port, name, strategy, results):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("strategy", ["replicated", "sharded"])
-@pytest.mark.parametrize("name", ["tiny", "qwen35-e16-t4", "graph-routes"])
-def test_two_rank_expert_parallel_matches_single_process(oracle, name, strategy):
-    world = 2
+@pytest.mark.parametrize(
+    "name, strategy, world",
+    [(name, strategy, 2) for name in ("tiny", "qwen35-e16-t4", "graph-routes")
+     for strategy in ("replicated", "sharded")]
+    + [("qwen35-e16-t4", "replicated", 4), ("qwen35-e16-t4", "sharded", 4)],
+)
+def test_expert_parallel_ranks_match_single_process(oracle, name, strategy, world):
     manager = mp.Manager()
     results = manager.dict()
     mp.spawn(_worker, args=(world, _free_port(), name, strategy, results), nprocs=world,
