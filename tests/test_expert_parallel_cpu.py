@@ -2,7 +2,7 @@
 
 Checks the host logic of `cfm_b200.reader.expert_parallel` (expert placement,
 dispatch, score or selection exchange, combine) for both strategies without a
-GPU: every rank holds half of the experts and half of the tokens; results must
+GPU: every rank holds an equal share of the experts and of the tokens; results must
 equal the single-process oracle on the whole layer (selections exactly, outputs
 to FP32 re-association).
 """
