@@ -70,6 +70,7 @@ struct Workspace {
 struct Layer {  // device-visible copy of cfm_layer with typed pointers
   int H, I, E, K, F, KEEP, R, activation, score, global_experts, owner, tensor_engine;
   int B, N, W;  // blocks, candidates, sketch words per coordinate
+  uint32_t width_magic;  // floor(2^32 / I) + 1, or 0 where the multiplication is not exact
   const __nv_bfloat16* gate_up;
   const __nv_bfloat16* down;
   const uint32_t* sketch;
@@ -84,6 +85,12 @@ struct Layer {  // device-visible copy of cfm_layer with typed pointers
   double* read_work;
   const float* threshold;  // device scalar of the threshold mode, or nullptr
 };
+
+// Slot of candidate i, i / I, by multiplication where that is exact for the layer.
+__device__ __forceinline__ int slot_of(const Layer& L, int i) {
+  return L.width_magic ? static_cast<int>(__umulhi(static_cast<uint32_t>(i), L.width_magic))
+                       : i / L.I;
+}
 
 // Score of candidate i (slot's channel c of local expert e) of token t; defined with the select kernel.
 __device__ __forceinline__ float candidate_score(const Layer& L, const Workspace& ws, int t, int i,
@@ -202,6 +209,10 @@ static Layer device_layer(const cfm_layer* l) {
   d.B = d.H / kBlock;
   d.N = d.K * d.I;
   d.W = 2 * d.I / kWordRows;
+  // i / I == umulhi(i, magic) for every candidate i < N as long as N * I <= 2^32.
+  const uint64_t width = static_cast<uint64_t>(d.I);
+  d.width_magic = static_cast<uint64_t>(d.N) * width <= (1ull << 32)
+                      ? static_cast<uint32_t>((1ull << 32) / width + 1) : 0u;
   d.gate_up = static_cast<const __nv_bfloat16*>(l->gate_up);
   d.down = static_cast<const __nv_bfloat16*>(l->down);
   d.sketch = l->sketch;
@@ -1194,7 +1205,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     } else {
       // Score every candidate from its sketch projections (zero for remote slots).
       for (int i = tid; i < N; i += kSelectThreads) {
-        const int slot = i / I, c = i - slot * I;
+        const int slot = slot_of(L, i), c = i - slot * I;
         const int e = ws.ids[static_cast<size_t>(t) * K + slot];
         float value = 0.0f;
         if (e >= 0)
@@ -1309,7 +1320,8 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
   if (budgets) {
     int running = ties_before;
     for (int i = begin; i < end; ++i) {
-      if (i % I == 0) s_tie_start[i / I] = running;
+      const int slot = slot_of(L, i);
+      if (i == slot * I) s_tie_start[slot] = running;
       running += screened && keys[i] == cut;
     }
     if (tid == 0) s_tie_start[K] = all_counted & 0xffff;
@@ -1330,7 +1342,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     __syncthreads();
   }
   auto keeps = [&](int i, int running) {
-    const int slot = i / I;
+    const int slot = slot_of(L, i);
     if (cut_given && route[slot] < 0) return false;  // another rank's slot
     if (!screened) return true;
     const uint32_t k = keys[i];
@@ -1356,7 +1368,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     for (int i = begin; i < end; ++i) {
       const bool keep = keeps(i, running);
       running += screened && keys[i] == cut;
-      const int slot = i / I;
+      const int slot = slot_of(L, i);
       if (i - slot * I == 0) s_starts[slot] = position;
       selected[i] = keep;
       completed[i] = keep && route[slot] >= 0;
