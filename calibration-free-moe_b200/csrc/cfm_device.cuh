@@ -18,7 +18,7 @@ namespace cfm {
 constexpr int kBlock = 128;          // coordinates per rotation block
 constexpr int kWordRows = 16;        // sketch rows per 32-bit word
 constexpr int kQuantBits = 21;       // block maximum maps into [2^21, 2^22]
-constexpr int kDownTileRows = 128;   // kept rows per down tile
+constexpr int kDownTileRows = 64;    // kept rows per down tile
 constexpr int kEncodeTileRows = 256; // channels per encoder tile
 constexpr unsigned kFull = 0xffffffffu;
 

@@ -1551,19 +1551,25 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
 // ---------------------------------------------------------------------------
 // down: gathered channel-major down rows
 // ---------------------------------------------------------------------------
-// grid (ceil(H / COLS), down_tiles, T), 128 threads = GROUPS row groups x
-// 128 / GROUPS lanes of 8 columns, COLS = 1024 / GROUPS.  One CTA sums up to
-// 128 kept rows of one expert over COLS columns with eight 16-byte loads in
-// flight per thread.  GROUPS = 8 (128 columns per CTA) measured fastest at every
-// batch size on B200: it gives the most CTAs and the shortest per-thread chains.
-template <int GROUPS, bool STRIDED>
-__global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8_t* padding) {
-  constexpr int LANES = 128 / GROUPS, COLS = LANES * 8;
+constexpr int kDownColumns = 1024;  // output columns per CTA: 32 accumulators per lane
+
+// grid (ceil(H / 1024), tiles, T), 128 threads.  One CTA sums up to 64 kept rows
+// of one expert, each scaled by its activation, over 1024 output columns.  A warp
+// takes every fourth row of the tile: per row a lane issues four 16-byte loads
+// 512 bytes apart (2 KiB contiguous per warp and row) at immediate offsets from
+// one address, with the next two rows' loads in flight while the current row is
+// accumulated into 32 FP32 registers.  The four warps' sums are added in warp
+// order through shared memory.  Under expert parallelism
+// (STRIDED) fewer CTAs than tiles are launched per token, since a rank owns few
+// of a token's slots; they walk the tiles in strides.
+template <bool STRIDED>
+__global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const uint8_t* padding) {
+  constexpr int CHUNKS = kDownColumns / 256;  // 16-byte pieces per lane and row
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
-  __shared__ float red[GROUPS > 1 ? GROUPS : 1][GROUPS > 1 ? COLS : 1];
+  __shared__ __align__(16) float red[4][kDownColumns];
   __shared__ int s_slot, s_first;
-  const int t = blockIdx.z, tid = threadIdx.x;
+  const int t = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (padding && padding[t]) return;
   const size_t token_pairs = static_cast<size_t>(t) * L.K;
   int used;
@@ -1574,88 +1580,98 @@ __global__ void __launch_bounds__(128) k_down(Layer L, Workspace ws, const uint8
         ws.ids[last] >= 0 ? (ws.counts[last] + kDownTileRows - 1) / kDownTileRows : 0;
     used = ws.tile_starts[last] + tail;
   }
-  // Under expert parallelism (STRIDED) fewer CTAs than tiles are launched per token,
-  // since a rank owns few of a token's slots; they walk the tiles in strides.
   int tile = blockIdx.y;
   if (tile >= used) return;
+  const int column0 = blockIdx.x * kDownColumns + lane * 8;  // this lane's first column
   do {
-  if (tid == 0) s_slot = -1;
-  __syncthreads();
-  if (tid < L.K) {  // the slot whose tile range holds this tile, if any
-    const int e = ws.ids[token_pairs + tid];
-    const int tiles =
-        e >= 0 ? (ws.counts[token_pairs + tid] + kDownTileRows - 1) / kDownTileRows : 0;
-    const int begin = ws.tile_starts[token_pairs + tid];
-    if (tile >= begin && tile < begin + tiles) {
-      s_slot = tid;
-      s_first = (tile - begin) * kDownTileRows;
+    if (tid == 0) s_slot = -1;
+    __syncthreads();
+    if (tid < L.K) {  // the slot whose tile range holds this tile, if any
+      const int e = ws.ids[token_pairs + tid];
+      const int tiles =
+          e >= 0 ? (ws.counts[token_pairs + tid] + kDownTileRows - 1) / kDownTileRows : 0;
+      const int begin = ws.tile_starts[token_pairs + tid];
+      if (tile >= begin && tile < begin + tiles) {
+        s_slot = tid;
+        s_first = (tile - begin) * kDownTileRows;
+      }
     }
-  }
-  __syncthreads();
-  const int slot = s_slot, first = s_first;
-  if (STRIDED) __syncthreads();  // all have read the slot before the next tile resets it
-  if (slot < 0) continue;  // uniform: every thread read the same slot
-  const int e = ws.ids[token_pairs + slot];
-  const int rows = min(kDownTileRows, ws.counts[token_pairs + slot] - first);
-  const int32_t* list =
-      ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first;
-  const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
-  if (tid < rows) {
-    const int cid = list[tid];
-    tile_channel[tid] = cid - slot * L.I;
-    tile_activation[tid] = __bfloat162float(act[cid]);
-  }
-  __syncthreads();
-  const int group = tid / LANES, lane = tid - group * LANES;
-  const int col = blockIdx.x * COLS + lane * 8;
-  const bool inside = col < L.H;
-  const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + (inside ? col : 0);
-  float acc[8];
+    __syncthreads();
+    const int slot = s_slot, first = s_first;
+    if (slot < 0) continue;  // uniform: every thread read the same slot
+    const int e = ws.ids[token_pairs + slot];
+    const int rows = min(kDownTileRows, ws.counts[token_pairs + slot] - first);
+    const int32_t* list =
+        ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first;
+    const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
+    if (tid < rows) {
+      const int cid = list[tid];
+      tile_channel[tid] = cid - slot * L.I;
+      tile_activation[tid] = __bfloat162float(act[cid]);
+    }
+    __syncthreads();
+    const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + column0;
+    bool live[CHUNKS];
 #pragma unroll
-  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-  constexpr int U = 8;  // rows in flight per thread
-  for (int r0 = group; r0 < rows; r0 += GROUPS * U) {
-    uint4 w[U];
-    float a[U];
+    for (int j = 0; j < CHUNKS; ++j) live[j] = column0 + 256 * j < L.H;
+    float acc[CHUNKS][8];
 #pragma unroll
-    for (int k = 0; k < U; ++k) {
-      const int r = min(r0 + GROUPS * k, rows - 1);
-      a[k] = r0 + GROUPS * k < rows ? tile_activation[r] : 0.0f;
-      w[k] = load_stream16(base + static_cast<size_t>(tile_channel[r]) * L.H);
+    for (int j = 0; j < CHUNKS; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[j][i] = 0.0f;
+    auto fetch = [&](int r, uint4 (&w)[CHUNKS]) {
+      const __nv_bfloat16* row = base + static_cast<size_t>(tile_channel[r]) * L.H;
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j)
+        w[j] = live[j] ? load_stream16(row + 256 * j) : make_uint4(0, 0, 0, 0);
+    };
+    auto add = [&](int r, const uint4 (&w)[CHUNKS]) {
+      const float a = tile_activation[r];
+#pragma unroll
+      for (int j = 0; j < CHUNKS; ++j) {
+        acc[j][0] = fmaf(bf16_lo(w[j].x), a, acc[j][0]);
+        acc[j][1] = fmaf(bf16_hi(w[j].x), a, acc[j][1]);
+        acc[j][2] = fmaf(bf16_lo(w[j].y), a, acc[j][2]);
+        acc[j][3] = fmaf(bf16_hi(w[j].y), a, acc[j][3]);
+        acc[j][4] = fmaf(bf16_lo(w[j].z), a, acc[j][4]);
+        acc[j][5] = fmaf(bf16_hi(w[j].z), a, acc[j][5]);
+        acc[j][6] = fmaf(bf16_lo(w[j].w), a, acc[j][6]);
+        acc[j][7] = fmaf(bf16_hi(w[j].w), a, acc[j][7]);
+      }
+    };
+    // Three row buffers used in turn: two rows' loads fly while one is added.
+    uint4 first_row[CHUNKS], second_row[CHUNKS], third_row[CHUNKS];
+    if (warp < rows) fetch(warp, first_row);
+    if (warp + 4 < rows) fetch(warp + 4, second_row);
+    for (int r = warp; r < rows; r += 12) {
+      if (r + 8 < rows) fetch(r + 8, third_row);
+      add(r, first_row);
+      if (r + 12 < rows) fetch(r + 12, first_row);
+      if (r + 4 < rows) add(r + 4, second_row);
+      if (r + 16 < rows) fetch(r + 16, second_row);
+      if (r + 8 < rows) add(r + 8, third_row);
     }
 #pragma unroll
-    for (int k = 0; k < U; ++k) {
-      acc[0] = fmaf(bf16_lo(w[k].x), a[k], acc[0]);
-      acc[1] = fmaf(bf16_hi(w[k].x), a[k], acc[1]);
-      acc[2] = fmaf(bf16_lo(w[k].y), a[k], acc[2]);
-      acc[3] = fmaf(bf16_hi(w[k].y), a[k], acc[3]);
-      acc[4] = fmaf(bf16_lo(w[k].z), a[k], acc[4]);
-      acc[5] = fmaf(bf16_hi(w[k].z), a[k], acc[5]);
-      acc[6] = fmaf(bf16_lo(w[k].w), a[k], acc[6]);
-      acc[7] = fmaf(bf16_hi(w[k].w), a[k], acc[7]);
+    for (int j = 0; j < CHUNKS; ++j) {
+      float4* mine = reinterpret_cast<float4*>(&red[warp][256 * j + lane * 8]);
+      mine[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+      mine[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
     }
-  }
-  float* parts = ws.down_parts + (static_cast<size_t>(t) * ws.down_tiles + tile) * L.H;
-  if (GROUPS == 1) {
-    if (inside) {
-      float4* out = reinterpret_cast<float4*>(parts + col);
-      out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-      out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    __syncthreads();
+    float* parts = ws.down_parts + (static_cast<size_t>(t) * ws.down_tiles + tile) * L.H +
+                   blockIdx.x * kDownColumns;
+    for (int c = tid * 4; c < kDownColumns; c += 128 * 4) {
+      if (blockIdx.x * kDownColumns + c < L.H) {
+        const float4 a = *reinterpret_cast<const float4*>(&red[0][c]);
+        const float4 b = *reinterpret_cast<const float4*>(&red[1][c]);
+        const float4 d = *reinterpret_cast<const float4*>(&red[2][c]);
+        const float4 g = *reinterpret_cast<const float4*>(&red[3][c]);
+        *reinterpret_cast<float4*>(parts + c) =
+            make_float4(((a.x + b.x) + d.x) + g.x, ((a.y + b.y) + d.y) + g.y,
+                        ((a.z + b.z) + d.z) + g.z, ((a.w + b.w) + d.w) + g.w);
+      }
     }
-    continue;
-  }
-  float4* mine = reinterpret_cast<float4*>(&red[GROUPS > 1 ? group : 0][GROUPS > 1 ? lane * 8 : 0]);
-  mine[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-  mine[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
-  __syncthreads();
-  for (int c = tid; c < COLS; c += 128) {
-    if (blockIdx.x * COLS + c < L.H) {
-      float sum = 0.0f;
-#pragma unroll
-      for (int g2 = 0; g2 < GROUPS; ++g2) sum += red[GROUPS > 1 ? g2 : 0][GROUPS > 1 ? c : 0];
-      parts[blockIdx.x * COLS + c] = sum;
-    }
-  }
+    // The barrier at the top of the next tile orders these reads before its writes.
   } while (STRIDED && (tile += gridDim.y) < used);
 }
 
@@ -2129,11 +2145,11 @@ static int run_down(const Bound& b) {
     const int64_t share = (2LL * tiles * b.L.E + b.L.global_experts - 1) / b.L.global_experts;
     tiles = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(tiles, share)));
   }
-  const dim3 grid(b.L.H / 128, tiles, b.T);
+  const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, tiles, b.T);
   if (tiles < b.ws.down_tiles)
-    k_down<8, true><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+    k_down<true><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
   else
-    k_down<8, false><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
+    k_down<false><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
   return launched();
 }
 
