@@ -50,8 +50,8 @@ KERNEL_OF_STAGE = {
 # workload only.
 NCU_DRAM_BYTES = {
     ("qwen3-30b-a3b", 64): {
-        "k_screen": 108.2e6, "k_exact": 344.4e6, "k_down": 158.7e6, "k_encode": 15.8e6,
-        "k_select": 3.6e6, "k_output": 5.8e6, "k_prepare": 0.3e6,
+        "k_screen": 108.2e6, "k_exact": 344.4e6, "k_down": 160.6e6, "k_encode": 15.8e6,
+        "k_select": 3.6e6, "k_output": 8.6e6, "k_prepare": 0.3e6,
     },
 }
 
