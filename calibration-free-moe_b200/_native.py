@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 8
+ABI_VERSION = 9
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -201,6 +201,8 @@ class StaticScreen(ctypes.Structure):
         ("exponents", ctypes.c_void_p),
         ("padding", ctypes.c_void_p),
         ("partial", ctypes.c_void_p),
+        ("energies", ctypes.c_void_p),
+        ("variances", ctypes.c_void_p),
     ]
 
 

@@ -98,13 +98,17 @@ __device__ __forceinline__ float candidate_score(const Layer& L, const Workspace
 
 static int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
+// Most candidates per token (N = K * I) the selection kernels take: their scans pack two
+// counts of at most N into the halves of one 32-bit integer.
+constexpr int64_t kMaxCandidates = 32767;
+
 static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layout* o) {
   if (!l || !o) return CFM_E_NULL;
   const int64_t H = l->hidden, I = l->width, K = l->top_k, F = l->final_count;
   const int64_t KEEP = l->keep, R = l->rank, C = capacity;
   if (H <= 0 || H % kBlock || I <= 0 || I % 16 || K <= 0 || K > 32 || KEEP < 1 ||
       KEEP > kBlock || R < 0 || R > 256 || (R % 8) || (R && (256 % R)) || F < 1 ||
-      F > K * I || K * I > 65535 * 16)
+      F > K * I || K * I > kMaxCandidates)
     return CFM_E_SHAPE;
   if (C < 1) return CFM_E_CAPACITY;
   const int64_t B = H / kBlock, N = K * I;
@@ -2175,9 +2179,11 @@ static int run_output(const Bound& b, const cfm_call* call) {
 struct SideStream {
   cudaStream_t stream;
   cudaEvent_t fork, join;
+  std::mutex* sequence;  // held while a whole-layer call enqueues its fork .. join sequence
   bool ready;
 };
 static SideStream g_side[64];
+static std::mutex g_side_sequence[64];
 static std::mutex g_side_lock;
 
 static int side_stream(SideStream* out) {
@@ -2197,6 +2203,7 @@ static int side_stream(SideStream* out) {
       (void)cudaGetLastError();
       return -1;
     }
+    slot.sequence = &g_side_sequence[device];
     slot.ready = true;
   }
   *out = slot;
@@ -2293,18 +2300,43 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
   if (!layer->gate_up || !layer->down) return CFM_E_NULL;
   SideStream side;
   const bool have_side = b.L.F < b.L.N && side_stream(&side) == 0;
+  // The side stream and its two events are shared by every whole-layer call on the
+  // device: the enqueue sequence below runs under the device's lock, so calls from
+  // several host threads do not interleave their fork and join points.
+  std::unique_lock<std::mutex> sequence;
+  if (have_side) sequence = std::unique_lock<std::mutex>(*side.sequence);
+  // After a fork the caller's stream must wait for the side stream again whatever
+  // happens, or a capture of the caller's stream would be left with an unjoined branch.
+  bool forked = false;
+  auto leave = [&](int code) {
+    if (forked) {
+      (void)cudaEventRecord(side.join, side.stream);
+      (void)cudaStreamWaitEvent(b.stream, side.join, 0);
+      forked = false;
+    }
+    return code;
+  };
+  auto fork_side = [&]() {
+    cudaError_t err = cudaEventRecord(side.fork, b.stream);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(side.stream, side.fork, 0);
+    if (err == cudaSuccess) forked = true;
+    return static_cast<int>(err);
+  };
+  auto join_side = [&]() {
+    cudaError_t err = cudaEventRecord(side.join, side.stream);
+    if (err == cudaSuccess) err = cudaStreamWaitEvent(b.stream, side.join, 0);
+    forked = false;
+    return static_cast<int>(err);
+  };
+  Bound on_side = b;
+  if (have_side) on_side.stream = side.stream;
   if (have_side && !call->input_prepared) {
     // Routing (and the grouping by expert) does not depend on the rotated input:
     // it runs on the side stream beside the rotation.
-    cudaError_t err = cudaEventRecord(side.fork, b.stream);
-    if (err == cudaSuccess) err = cudaStreamWaitEvent(side.stream, side.fork, 0);
-    if (err != cudaSuccess) return static_cast<int>(err);
-    Bound on_side = b;
-    on_side.stream = side.stream;
-    if ((rc = run_route(on_side, call))) return rc;
-    if ((err = cudaEventRecord(side.join, side.stream)) != cudaSuccess) return static_cast<int>(err);
-    if ((rc = run_prepare(b, call))) return rc;
-    if ((err = cudaStreamWaitEvent(b.stream, side.join, 0)) != cudaSuccess) return static_cast<int>(err);
+    if ((rc = fork_side())) return leave(rc);
+    if ((rc = run_route(on_side, call))) return leave(rc);
+    if ((rc = run_prepare(b, call))) return leave(rc);
+    if ((rc = join_side())) return leave(rc);
   } else {
     if (!call->input_prepared && (rc = run_prepare(b, call))) return rc;
     if ((rc = run_route(b, call))) return rc;
@@ -2315,19 +2347,13 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
   // HBM-bound gathers on the side stream and joins before the output mix.
   const bool fork = b.L.R > 0 && have_side;
   if (fork) {
-    cudaError_t err = cudaEventRecord(side.fork, b.stream);
-    if (err == cudaSuccess) err = cudaStreamWaitEvent(side.stream, side.fork, 0);
-    if (err != cudaSuccess) return static_cast<int>(err);
-    Bound on_side = b;
-    on_side.stream = side.stream;
-    if ((rc = run_encode(on_side))) return rc;
-    if ((err = cudaEventRecord(side.join, side.stream)) != cudaSuccess) return static_cast<int>(err);
+    if ((rc = fork_side())) return leave(rc);
+    if ((rc = run_encode(on_side))) return leave(rc);
   }
-  if ((rc = run_exact(b, call))) return rc;
-  if ((rc = run_down(b))) return rc;
+  if ((rc = run_exact(b, call))) return leave(rc);
+  if ((rc = run_down(b))) return leave(rc);
   if (fork) {
-    const cudaError_t err = cudaStreamWaitEvent(b.stream, side.join, 0);
-    if (err != cudaSuccess) return static_cast<int>(err);
+    if ((rc = join_side())) return leave(rc);
   } else if ((rc = run_encode(b))) {
     return rc;
   }
@@ -2424,6 +2450,15 @@ extern "C" int cfm_screen_static(const cfm_layer* layer, const cfm_static_screen
   const cudaError_t err = cudaMemsetAsync(scratch.counters, 0, sizeof(unsigned int) * pairs,
                                           b.stream);
   if (err != cudaSuccess) return static_cast<int>(err);
+  // The recovery-aware score also reads the residual variances of the projections;
+  // that kernel needs no scratch and runs when the caller asks for them.
+  if (io->variances) {
+    if (!io->energies) return CFM_E_NULL;
+    b.ws.norms = const_cast<float*>(io->energies);
+    b.ws.variances = io->variances;
+    k_variance<<<dim3(b.T * L.K, (2 * L.I + 255) / 256), 256, 0, b.stream>>>(b.L, b.ws, b.padding);
+    if ((rc = launched())) return rc;
+  }
   // Always split the rotation blocks across CTAs, so the scratch is what joins them.
   int S = 2;
   while (S < L.B && pairs * S < 2 * 148) S *= 2;
@@ -2437,4 +2472,3 @@ extern "C" int cfm_screen_static(const cfm_layer* layer, const cfm_static_screen
     default: return launch_screen<1>(b, S);
   }
 }
-

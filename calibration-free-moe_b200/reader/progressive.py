@@ -267,6 +267,9 @@ class ProgressiveReader:
             raise ValueError(f"Unsupported routed expert activation: {activation}")
         if screen_block_splits not in (1, 2, 4, 8) or grouped_screen_splits not in (1, 2, 4, 8):
             raise ValueError("Screen block splits must be 1, 2, 4 or 8")
+        # The contract check below and the error texts of this constructor restate the
+        # reference's (progressive.py:3234-3271, 3310, 3328, 3407): callers and the
+        # reference's tests match on which inputs are rejected and on the messages.
         if (
             gate_up.shape != (e, 2 * i, h)
             or down.shape != (e, h, i)
@@ -584,6 +587,19 @@ class ProgressiveReader:
                 dist.all_reduce(self.latent[:tokens], group=self.ep_group)
             self._stage("cfm_output", call)
         return out
+
+    def check_status(self) -> None:
+        """Raise if a kernel of this reader's workspace reported a device-side error.
+
+        The tensor-memory screen (`tensor_engine="tcgen05"`) bounds every barrier wait;
+        a wait that runs out sets a flag in the workspace and leaves the projections
+        of that call unwritten, so the kept channels of that call are not to be
+        trusted.  Reading the flag synchronises with the device: call this at points
+        where the host waits anyway (after a decode step, before reading a report).
+        """
+        status = self.workspace.status.cpu().tolist()
+        if any(status):
+            raise RuntimeError(f"reader kernels reported a device-side error: status {status}")
 
     # ------------------------------------------------------------------
     def report(self) -> dict[str, float | None]:

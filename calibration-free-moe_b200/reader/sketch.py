@@ -6,6 +6,12 @@ follow the reference's `calibration_free_moe/reader/sketch.py`
 (`block_hadamard_signs` :22, `rotate_blocks` :38, `mask_rotated_blocks` :53,
 `require_sketch_acquisition` :71, `build_sketch` :84, `unpack_sketch` :209).
 
+`rotate_blocks`, `mask_rotated_blocks` and `require_sketch_acquisition` restate the
+reference's functions of the same names: the butterfly's stage order, the tie rule
+of the mask (equal magnitudes keep the lower coordinate) and the acquisition tag
+are the contract with banks and sketches built by the reference, so they leave
+no freedom beyond naming.
+
 Two storage layouts exist here:
 
 * the reference layout, five trits per byte in coordinate-major 32-byte tiles,

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 8
+#define CFM_ABI_VERSION 9
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -267,6 +267,10 @@ typedef struct cfm_static_screen {
   const int32_t* exponents;   /* i32 [T, B, 2] exponent and sum per block        */
   const uint8_t* padding;     /* bool [T] or NULL                                */
   float* partial;             /* out: f32 [T, 2, N] sketch projections           */
+  const float* energies;      /* f32 [T, B] energy of the kept coordinates per block
+                                 (the workspace's `norms`); needed with `variances` */
+  float* variances;           /* out: f32 [T, 2, N] residual variances of the
+                                 projections, or NULL to skip them               */
 } cfm_static_screen;
 
 /* The split screen (one GEMV per (token, expert) pair, rotation blocks spread
@@ -280,12 +284,21 @@ typedef struct cfm_static_screen {
  *
  * Limits: T * K <= CFM_STATIC_MAX_PAIRS and T * K * B * 2I <=
  * CFM_STATIC_PARTS_FLOATS, else CFM_E_STATIC_CAPACITY and nothing is launched.
- * The first call on a device looks up the arrays' device addresses; make that
- * call once, with the device current, before any stream capture begins.  All
- * calls on a device share the arrays, which keep the previous call's contents:
- * the counters are cleared on the stream at the start of every call, and two
- * calls whose kernels overlap on the GPU (different streams) race.
- * Results equal cfm_screen's bit for bit.
+ * The arrays are part of the library's device image: the CUDA runtime reserves
+ * them when it loads that image on a device, which happens at the latest on the
+ * first call of any entry point there.  A host whose memory pool takes all free
+ * device memory must therefore load the library and make one call on the device
+ * BEFORE the pool grabs its memory; from then on no call changes the amount of
+ * free device memory.  The first call on a device also looks up the arrays'
+ * device addresses; make it once, with the device current, before any stream
+ * capture begins.  All calls on a device share the arrays, which keep the previous
+ * call's contents: the counters are cleared on the stream at the start of every
+ * call, and two calls whose kernels overlap on the GPU (different streams) race.
+ * `partial` equals what cfm_screen writes, bit for bit.  cfm_screen on a layer with
+ * the recovery-aware score also fills the workspace's `variances`, which
+ * cfm_select and cfm_score then read: pass `energies` and `variances` to get them
+ * from this call too (that kernel needs no scratch); with `variances` NULL only
+ * `partial` is written and such a caller must provide the variances itself.
  * No counterpart in the reference, whose scratch is always caller-allocated
  * (ReaderWorkspace). */
 int cfm_screen_static(const cfm_layer* layer, const cfm_static_screen* io, void* stream);

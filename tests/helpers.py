@@ -20,8 +20,12 @@ def golden(name: str) -> dict:
 
 
 def prepared(name: str) -> dict:
+    """A named case's inputs plus its CPU-built sketch and channel-major down weight."""
+    return prepared_case(cases.build(name))
+
+
+def prepared_case(case) -> dict:
     """A case's inputs plus its CPU-built sketch and channel-major down weight."""
-    case = cases.build(name)
     signs = block_hadamard_signs(case.plan.hidden_size, "cpu")
     codes, statistics = build_sketch(case.gate_up, signs)
     down = channel_major_down(case.down)

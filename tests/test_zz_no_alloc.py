@@ -8,7 +8,8 @@ forbids allocator calls.  For them the library keeps the split screen's scratch
 test calls that entry point through the C ABI, twice in a row on the same
 inputs, and requires both results to equal the regular `cfm_screen` output bit
 for bit (the bar of the other parity tests); the second call proves that what
-the first left in the shared arrays does not leak into the next result.
+the first left in the shared arrays does not leak into the next result, and the
+amount of free device memory is the same before and after it.
 
 Collected last on purpose, so a run that stops at the first failure has already
 covered every other test.
@@ -26,7 +27,7 @@ from test_gpu_parity import make_reader, run_reader
 pytestmark = pytest.mark.gpu
 
 
-def call_static(reader, tokens, out, padding=None):
+def call_static(reader, tokens, out, padding=None, variances=None):
     w = reader.workspace
     io = _native.StaticScreen()
     io.tokens = tokens
@@ -36,6 +37,9 @@ def call_static(reader, tokens, out, padding=None):
     io.exponents = w.exponents.data_ptr()
     io.padding = padding.data_ptr() if padding is not None else None
     io.partial = out.data_ptr()
+    if variances is not None:
+        io.energies = w.norms.data_ptr()
+        io.variances = variances.data_ptr()
     stream = torch.cuda.current_stream().cuda_stream
     return _native.screen_static()(
         ctypes.byref(reader._layer), ctypes.byref(io), ctypes.c_void_p(stream)
@@ -49,11 +53,51 @@ def test_static_scratch_screen_matches_regular_screen_twice():
     tokens = item["case"].hidden.shape[0]
     expected = reader.partial[:tokens].clone()
     assert torch.isfinite(expected).all() and expected.abs().sum() > 0
-    for _ in range(2):
+    for repeat in range(2):
         out = torch.full_like(expected, float("nan"))
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         assert call_static(reader, tokens, out) == 0
         torch.cuda.synchronize()
+        if repeat:  # the first call on a device may still load the library's device image
+            assert torch.cuda.mem_get_info()[0] == free_before
         assert torch.equal(out, expected)
+
+
+def test_static_scratch_screen_matches_the_expert_major_screen():
+    """Sixteen tokens: the regular screen runs expert-major on the tensor cores, the
+    library-scratch screen per (token, expert) pair; same bits."""
+    import cases
+    from helpers import prepared_case
+
+    item = prepared_case(cases._random("static-t16", 421, 256, 96, 8, 4, 16, 16, 0.125, 0.625))
+    reader = make_reader(item)
+    run_reader(reader, item["case"])
+    expected = reader.partial[:16].clone()
+    assert expected.abs().sum() > 0
+    out = torch.full_like(expected, float("nan"))
+    assert call_static(reader, 16, out) == 0
+    torch.cuda.synchronize()
+    free_before = torch.cuda.mem_get_info()[0]
+    assert call_static(reader, 16, out) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before
+    assert torch.equal(out, expected)
+
+
+def test_static_scratch_screen_also_gives_the_variances():
+    """Recovery-aware score: the variances cfm_screen leaves for the selection come from
+    the library-scratch call too when asked for."""
+    item = prepared("gh-keep80-gelu")
+    reader = make_reader(item)
+    run_reader(reader, item["case"])
+    tokens = item["case"].hidden.shape[0]
+    expected, spread = reader.partial[:tokens].clone(), reader.variances[:tokens].clone()
+    assert spread.abs().sum() > 0
+    out, variances = torch.full_like(expected, float("nan")), torch.full_like(spread, float("nan"))
+    assert call_static(reader, tokens, out, variances=variances) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(out, expected) and torch.equal(variances, spread)
 
 
 def test_static_scratch_screen_with_padding_row():
