@@ -354,7 +354,7 @@ def triton_comparator(args) -> dict:
         if line.startswith("{"):
             result = json.loads(line)
             keep = ("value", "unit", "ms_per_step", "unavailable", "selection_agreement", "options",
-                    "config", "samples_ms_per_step")
+                    "failed_variants", "samples_ms_per_step")
             return {key: result[key] for key in keep if key in result}
     tail = (done.stderr or done.stdout).strip().splitlines()[-3:]
     return {"unavailable": "no result line; " + " | ".join(tail)[-400:]}
@@ -417,6 +417,7 @@ def run_triton(args, shape, plan) -> None:
         screen_keep=args.screen_keep if args.screen_keep is not None else shape.screen_keep,
     )
     options = {"selection_score": "point"}
+    errors: list = []
     try:
         weights_of_layer, batches = [], []
         for index in range(layers):
@@ -442,14 +443,25 @@ def run_triton(args, shape, plan) -> None:
             stream.synchronize()
 
         with torch.cuda.stream(stream):
-            try:
-                build_and_warm()
-            except Exception as error:  # noqa: BLE001
-                # Programmatic dependent launch is the one option that depends on the
-                # installed Triton; try once more without it before giving up.
-                options["pdl"] = False
-                options["first_error"] = f"{type(error).__name__}: {error}"[:300]
-                build_and_warm()
+            # The reference's scheduling options do not change its arithmetic
+            # (progressive.py:3199-3204).  Its defaults first; if a kernel does not build
+            # with the installed Triton, the variants that avoid that kernel, in turn.
+            variants = [
+                {},
+                {"pdl": False},
+                {"pdl": False, "grouped_screen_tokens": 1 << 20},
+                {"pdl": False, "grouped_screen_tokens": 1 << 20, "grouped_tokens": 1 << 20},
+            ]
+            for variant in variants:
+                options = {"selection_score": "point", **variant}
+                try:
+                    build_and_warm()
+                    break
+                except Exception as error:  # noqa: BLE001
+                    errors.append({"options": variant,
+                                   "error": f"{type(error).__name__}: {error}"[:1200]})
+                    if variant is variants[-1]:
+                        raise
             graphs = []
             for index in range(layers):
                 graph = torch.cuda.CUDAGraph()
@@ -476,14 +488,14 @@ def run_triton(args, shape, plan) -> None:
             "kept_per_token": plan.final_count,
         }
     except Exception as error:  # noqa: BLE001
-        print(json.dumps({**base, "options": options,
+        print(json.dumps({**base, "options": options, "failed_variants": errors,
                           "unavailable": f"{type(error).__name__}: {error}"[:600]}))
         return
     print(json.dumps({
         **base, "value": tokens / (step_ms * 1e-3), "ms_per_step": step_ms,
         "steps": count, "warmup": args.warmup, "samples_ms_per_step": [round(s, 5) for s in samples],
         "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "options": options,
-        "selection_agreement": agreement,
+        "failed_variants": errors, "selection_agreement": agreement,
     }))
 
 
@@ -500,8 +512,9 @@ def workload_config(shape, plan, tokens, layers, gpus) -> dict:
         "parallelism": "single GPU" if gpus == 1 else (
             f"expert parallel over {gpus} GPUs: {shape.experts // gpus} experts per rank, "
             f"{tokens} tokens per rank per step; sketch replicated, home-rank screen and "
-            "selection, all_gather of rows and kept-channel lists, FP32 reduce_scatter "
-            "combine (NCCL)"),
+            "selection, all_gather of hidden rows and router outputs (NCCL), kept-channel "
+            "lists and FP32 partial rows stored into the peers' memory by the library's "
+            "kernels (NVLink) unless --exchange collective"),
     }
 
 
@@ -603,13 +616,15 @@ def run_ours(args, shape, plans) -> None:
                 sharded.append(ExpertParallelReader(
                     gate_up, down, encoder, decoder, plan, capacity, global_experts=shape.experts,
                     selection_score="point", retain_reference_sketch=False, sketch=sketches[index],
+                    exchange=args.exchange,
                 ))
                 readers.append(sharded[-1].reader)
             else:
                 readers.append(ProgressiveReader(
                     gate_up, down, encoder, decoder, plan, capacity,
                     selection_score="point", retain_reference_sketch=False,
-                    tensor_engine=args.tensor_engine, sketch=sketches[index],
+                    tensor_engine=args.tensor_engine, row_engine=args.row_engine,
+                    sketch=sketches[index],
                 ))
         trace(f"layers built for {label}")
         for tokens in token_counts:
@@ -852,6 +867,11 @@ def main() -> None:
     parser.add_argument("--no-gpu-comparator", action="store_true")
     parser.add_argument("--tensor-engine", default="mma_sync", choices=("mma_sync", "tcgen05"),
                         help="tensor-core path of the expert-major screen")
+    parser.add_argument("--exchange", default="auto", choices=("auto", "peer", "collective"),
+                        help="expert parallel: kept lists and partial rows over peer memory "
+                             "or by NCCL collectives")
+    parser.add_argument("--row-engine", default="auto", choices=("auto", "per_token", "expert_major"),
+                        help="how batches of eight tokens and more read the native rows")
     args = parser.parse_args()
     shape = synthetic.CONFIGS[args.config]
 

@@ -15,7 +15,9 @@ from pathlib import Path
 
 PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
-HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE.parent / "include" / "cfm_b200.h"]
+HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE / "csrc" / "cfm_grouped.cuh",
+           PACKAGE / "csrc" / "cfm_exchange.cuh",
+           PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
 ABI_VERSION = 9
 
@@ -29,8 +31,14 @@ NVCC_FLAGS = [
 STAGES = (
     "cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_score", "cfm_select", "cfm_exact",
     "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_adopt", "cfm_reader_forward",
+    "cfm_exchange_send_lists",
 )
-SYMBOLS = ("cfm_abi_version", "cfm_error_string", "cfm_workspace_layout_for", "cfm_finish") + STAGES
+PEER_SYMBOLS = ("cfm_exchange_bytes", "cfm_peer_alloc", "cfm_peer_export", "cfm_peer_import",
+                "cfm_peer_release", "cfm_exchange_status", "cfm_finish_rows")
+SYMBOLS = (("cfm_abi_version", "cfm_error_string", "cfm_workspace_layout_for", "cfm_finish")
+           + STAGES + PEER_SYMBOLS)
+MAX_RANKS = 16
+PEER_HANDLE_BYTES = 64
 
 
 class Layer(ctypes.Structure):
@@ -49,6 +57,8 @@ class Layer(ctypes.Structure):
         ("global_experts", ctypes.c_int32),
         ("recovery_owner", ctypes.c_int32),
         ("tensor_engine", ctypes.c_int32),
+        ("row_engine", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
         ("gate_up", ctypes.c_void_p),
         ("down", ctypes.c_void_p),
         ("sketch", ctypes.c_void_p),
@@ -81,6 +91,19 @@ class Call(ctypes.Structure):
         ("padding", ctypes.c_void_p),
         ("out", ctypes.c_void_p),
         ("lists", ctypes.c_void_p),
+        ("exchange", ctypes.c_void_p),
+    ]
+
+
+class Exchange(ctypes.Structure):
+    """`struct cfm_exchange`."""
+
+    _fields_ = [
+        ("world", ctypes.c_int32),
+        ("rank", ctypes.c_int32),
+        ("tokens", ctypes.c_int32),
+        ("reserved", ctypes.c_int32),
+        ("blocks", ctypes.c_void_p * MAX_RANKS),
     ]
 
 
@@ -168,6 +191,24 @@ def load() -> ctypes.CDLL:
     library.cfm_finish.restype = ctypes.c_int
     library.cfm_finish.argtypes = [
         ctypes.POINTER(Layer), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_void_p,
+    ]
+    library.cfm_exchange_bytes.restype = ctypes.c_int64
+    library.cfm_exchange_bytes.argtypes = [ctypes.POINTER(Layer), ctypes.c_int32, ctypes.c_int32]
+    library.cfm_peer_alloc.restype = ctypes.c_int
+    library.cfm_peer_alloc.argtypes = [ctypes.c_int64, ctypes.POINTER(ctypes.c_void_p)]
+    library.cfm_peer_export.restype = ctypes.c_int
+    library.cfm_peer_export.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+    library.cfm_peer_import.restype = ctypes.c_int
+    library.cfm_peer_import.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]
+    library.cfm_peer_release.restype = ctypes.c_int
+    library.cfm_peer_release.argtypes = [ctypes.c_void_p, ctypes.c_int32]
+    library.cfm_exchange_status.restype = ctypes.c_int
+    library.cfm_exchange_status.argtypes = [ctypes.POINTER(Exchange),
+                                            ctypes.POINTER(ctypes.c_int32)]
+    library.cfm_finish_rows.restype = ctypes.c_int
+    library.cfm_finish_rows.argtypes = [
+        ctypes.POINTER(Layer), ctypes.POINTER(Exchange), ctypes.c_void_p, ctypes.c_void_p,
         ctypes.c_void_p,
     ]
     _library = library

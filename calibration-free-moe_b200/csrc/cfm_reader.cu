@@ -23,6 +23,7 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace cfm {
@@ -68,7 +69,7 @@ struct Workspace {
 };
 
 struct Layer {  // device-visible copy of cfm_layer with typed pointers
-  int H, I, E, K, F, KEEP, R, activation, score, global_experts, owner, tensor_engine;
+  int H, I, E, K, F, KEEP, R, activation, score, global_experts, owner, tensor_engine, row_engine;
   int B, N, W;  // blocks, candidates, sketch words per coordinate
   uint32_t width_magic;  // floor(2^32 / I) + 1, or 0 where the multiplication is not exact
   const __nv_bfloat16* gate_up;
@@ -98,6 +99,9 @@ __device__ __forceinline__ float candidate_score(const Layer& L, const Workspace
 
 static int64_t align256(int64_t v) { return (v + 255) / 256 * 256; }
 
+// Most partial sums per (token, slot) the expert-major down kernel writes.
+constexpr int64_t kDownGroupedMaxParts = 8;
+
 // Most candidates per token (N = K * I) the selection kernels take: their scans pack two
 // counts of at most N into the halves of one 32-bit integer.
 constexpr int64_t kMaxCandidates = 32767;
@@ -119,7 +123,8 @@ static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layou
     return here;
   };
   o->parts_tokens = static_cast<int32_t>(C < 16 ? C : 16);
-  o->down_tiles = static_cast<int32_t>((F + kDownTileRows - 1) / kDownTileRows + K - 1);
+  o->down_tiles = static_cast<int32_t>(std::max<int64_t>(
+      (F + kDownTileRows - 1) / kDownTileRows + K - 1, kDownGroupedMaxParts * K));
   o->encoder_tiles = static_cast<int32_t>((I + kEncodeTileRows - 1) / kEncodeTileRows);
   o->reserved = 0;
   o->ids = take(4 * C * K);
@@ -210,6 +215,7 @@ static Layer device_layer(const cfm_layer* l) {
   d.global_experts = l->global_experts;
   d.owner = l->recovery_owner;
   d.tensor_engine = l->tensor_engine;
+  d.row_engine = l->row_engine;
   d.B = d.H / kBlock;
   d.N = d.K * d.I;
   d.W = 2 * d.I / kWordRows;
@@ -232,6 +238,8 @@ static Layer device_layer(const cfm_layer* l) {
   d.threshold = l->selection_threshold;
   return d;
 }
+
+#include "cfm_exchange.cuh"
 
 // ---------------------------------------------------------------------------
 // prepare: rotation, partial-screen mask, fixed-point copy
@@ -384,14 +392,26 @@ __global__ void __launch_bounds__(32) k_route(Layer L, Workspace ws, const void*
 // -1 after the last).  This rank orders and maps the router's experts exactly as
 // k_route does, keeps the entries of the slots it owns in their order, and
 // derives the per-slot counts, list starts and down-tile starts for them.
+// With `peers` the lists are those the home ranks stored into this rank's exchange
+// block; the CTA first waits (bounded) until the lists of its row's home rank have
+// landed for the current epoch.
 __global__ void __launch_bounds__(256) k_adopt(Layer L, Workspace ws, const void* ids, int ids64,
                                                const void* weights, int wbf16,
-                                               const uint8_t* padding, const int32_t* lists) {
+                                               const uint8_t* padding, const int32_t* lists,
+                                               Exchange x, int peers) {
   __shared__ int route[32];
   __shared__ int count[32];
   __shared__ int warp_total[8];
   const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const bool padded = padding && padding[t];
+  if (peers) {
+    uint32_t* header = exchange_header(x, x.rank);
+    if (tid == 0)
+      exchange_wait(header + kExchangeListsFlag + t / x.tokens, header[kExchangeEpoch] + 1u,
+                    header + kExchangeStatus, 1u);
+    lists = reinterpret_cast<const int32_t*>(x.block[x.rank] + exchange_lists_offset());
+    __syncthreads();
+  }
   if (warp == 0) {
     long long id = 0x7fffffffffffffffLL;
     float w = 0.0f;
@@ -428,7 +448,7 @@ __global__ void __launch_bounds__(256) k_adopt(Layer L, Workspace ws, const void
   int kept = 0;
   for (int base = 0; base < L.F; base += 256) {
     const int i = base + tid;
-    const int cid = i < L.F ? in[i] : -1;
+    const int cid = i < L.F ? __ldcg(in + i) : -1;  // past L1: a peer may have written it
     const int slot = cid >= 0 ? min(cid / L.I, L.K - 1) : 0;
     const bool keep = cid >= 0 && route[slot] >= 0;
     const unsigned ballot = __ballot_sync(kFull, keep);
@@ -1456,46 +1476,13 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
 // ---------------------------------------------------------------------------
 constexpr int kExactWarps = 4;
 
-// grid (ceil(F / 4), T), 128 threads; one warp per kept candidate.
-__global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace ws,
-                                                            const __nv_bfloat16* hidden,
-                                                            const uint8_t* padding) {
-  extern __shared__ uint4 xs[];  // H bf16 values of the token
-  const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (padding && padding[t]) return;
-  const int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * L.F;
-  const bool strided = gridDim.x * kExactWarps < L.F;  // CTAs walk the list in strides
-  if (L.expert_map) {
-    // Expert parallel: leave before staging the input when this CTA has nothing
-    // to do.  A list cut down to the local slots ends with -1 entries; a full list
-    // is probed for candidates of local experts.
-    if (list[blockIdx.x * kExactWarps] < 0) return;
-    if (!strided) {
-      const int probe = blockIdx.x * kExactWarps + warp;
-      bool mine = false;
-      if (probe < L.F) {
-        const int cid = list[probe];
-        mine = cid >= 0 && ws.ids[static_cast<size_t>(t) * L.K + cid / L.I] >= 0;
-      }
-      if (!__syncthreads_or(mine)) return;
-    }
-  }
-  const int chunks = L.H / 8;
-  const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
-  for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
-  __syncthreads();
-  for (int index = blockIdx.x * kExactWarps + warp; index < L.F;
-       index += gridDim.x * kExactWarps) {
-  const int cid = list[index];
-  if (cid < 0) break;  // lists end with -1 entries
-  const int slot = cid / L.I, c = cid - slot * L.I;
-  const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
-  if (e < 0) continue;
-  const uint4* gate = reinterpret_cast<const uint4*>(
-      L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
-  const uint4* up = gate + static_cast<size_t>(L.I) * L.H / 8;
+// One warp's dot products of a gate row and an up row with the input staged in
+// shared memory (`xs`, `chunks` 16-byte pieces): eight pieces of each row in
+// flight per lane (2048 columns per sweep), FP32 FMAs in a fixed order, then a
+// butterfly over the lanes.  Every lane returns the sums.
+__device__ __forceinline__ void exact_dot(const uint4* gate, const uint4* up, const uint4* xs,
+                                          int chunks, int lane, float& g_out, float& u_out) {
   float g = 0.0f, u = 0.0f;
-  // Eight 16-byte pieces of each row in flight per lane (2048 columns per sweep).
   constexpr int U = 8;
   for (int base = lane; base < chunks; base += 32 * U) {
     uint4 gw[U], uw[U];
@@ -1543,12 +1530,93 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
     g += __shfl_xor_sync(kFull, g, w);
     u += __shfl_xor_sync(kFull, u, w);
   }
+  g_out = g;
+  u_out = u;
+}
+
+// grid (ceil(F / 4), T), 128 threads; one warp per kept candidate.
+__global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace ws,
+                                                            const __nv_bfloat16* hidden,
+                                                            const uint8_t* padding) {
+  extern __shared__ uint4 xs[];  // H bf16 values of the token
+  const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (padding && padding[t]) return;
+  const int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * L.F;
+  const bool strided = gridDim.x * kExactWarps < L.F;  // CTAs walk the list in strides
+  if (L.expert_map) {
+    // Expert parallel: leave before staging the input when this CTA has nothing
+    // to do.  A list cut down to the local slots ends with -1 entries; a full list
+    // is probed for candidates of local experts.
+    if (list[blockIdx.x * kExactWarps] < 0) return;
+    if (!strided) {
+      const int probe = blockIdx.x * kExactWarps + warp;
+      bool mine = false;
+      if (probe < L.F) {
+        const int cid = list[probe];
+        mine = cid >= 0 && ws.ids[static_cast<size_t>(t) * L.K + cid / L.I] >= 0;
+      }
+      if (!__syncthreads_or(mine)) return;
+    }
+  }
+  const int chunks = L.H / 8;
+  const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
+  for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
+  __syncthreads();
+  for (int index = blockIdx.x * kExactWarps + warp; index < L.F;
+       index += gridDim.x * kExactWarps) {
+  const int cid = list[index];
+  if (cid < 0) break;  // lists end with -1 entries
+  const int slot = cid / L.I, c = cid - slot * L.I;
+  const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
+  if (e < 0) continue;
+  const uint4* gate = reinterpret_cast<const uint4*>(
+      L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
+  float g, u;
+  exact_dot(gate, gate + static_cast<size_t>(L.I) * L.H / 8, xs, chunks, lane, g, u);
   if (lane == 0) {
     ws.activations[static_cast<size_t>(t) * L.N + cid] =
         __float2bfloat16_rn(exact_feature(g, u, L.activation));
     ws.exact[static_cast<size_t>(t) * 2 * L.F + index] = g;
     ws.exact[static_cast<size_t>(t) * 2 * L.F + L.F + index] = u;
   }
+  }
+}
+
+// The same gather with the (token, expert) pairs walked in expert order:
+// grid (X, T * K), 128 threads.  CTA row y takes the y-th pair of the list
+// grouped by expert (k_group), so the tokens of one expert run next to each
+// other in time and a row several of them kept comes from HBM once and from L2
+// after that.  The X CTAs of a pair share its kept rows, one warp per row.  Same
+// arithmetic, same order, same bits as k_exact.
+__global__ void __launch_bounds__(kExactWarps * 32) k_exact_pairs(Layer L, Workspace ws,
+                                                                  const __nv_bfloat16* hidden) {
+  extern __shared__ uint4 xs[];  // H bf16 values of the token
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (static_cast<int>(blockIdx.y) >= ws.group_offsets[L.E]) return;
+  const int pair = ws.group_pairs[blockIdx.y];
+  const int count = ws.counts[pair];
+  if (static_cast<int>(blockIdx.x) * kExactWarps >= count) return;
+  const int t = pair / L.K, slot = pair - t * L.K, e = ws.ids[pair];
+  const int start = ws.starts[pair];
+  const int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * L.F + start;
+  const int chunks = L.H / 8;
+  const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
+  for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
+  __syncthreads();
+  for (int index = blockIdx.x * kExactWarps + warp; index < count;
+       index += gridDim.x * kExactWarps) {
+    const int cid = list[index];
+    const int c = cid - slot * L.I;
+    const uint4* gate = reinterpret_cast<const uint4*>(
+        L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
+    float g, u;
+    exact_dot(gate, gate + static_cast<size_t>(L.I) * L.H / 8, xs, chunks, lane, g, u);
+    if (lane == 0) {
+      ws.activations[static_cast<size_t>(t) * L.N + cid] =
+          __float2bfloat16_rn(exact_feature(g, u, L.activation));
+      ws.exact[static_cast<size_t>(t) * 2 * L.F + start + index] = g;
+      ws.exact[static_cast<size_t>(t) * 2 * L.F + L.F + start + index] = u;
+    }
   }
 }
 
@@ -1566,14 +1634,98 @@ constexpr int kDownColumns = 1024;  // output columns per CTA: 32 accumulators p
 // order through shared memory.  Under expert parallelism
 // (STRIDED) fewer CTAs than tiles are launched per token, since a rank owns few
 // of a token's slots; they walk the tiles in strides.
+// One tile: up to 64 kept rows of slot `slot` of token t, starting at position
+// `first` of the slot's part of the kept list, summed into down tile `tile`.
+// Called by all 128 threads of a CTA; begins and ends with the shared arrays free.
+__device__ __forceinline__ void down_tile(const Layer& L, const Workspace& ws, int t, int slot,
+                                          int first, int tile, int* tile_channel,
+                                          float* tile_activation, float (*red)[kDownColumns]) {
+  constexpr int CHUNKS = kDownColumns / 256;  // 16-byte pieces per lane and row
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const size_t token_pairs = static_cast<size_t>(t) * L.K;
+  const int column0 = blockIdx.x * kDownColumns + lane * 8;  // this lane's first column
+  const int e = ws.ids[token_pairs + slot];
+  const int rows = min(kDownTileRows, ws.counts[token_pairs + slot] - first);
+  const int32_t* list =
+      ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first;
+  const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
+  if (tid < rows) {
+    const int cid = list[tid];
+    tile_channel[tid] = cid - slot * L.I;
+    tile_activation[tid] = __bfloat162float(act[cid]);
+  }
+  __syncthreads();
+  const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + column0;
+  bool live[CHUNKS];
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) live[j] = column0 + 256 * j < L.H;
+  float acc[CHUNKS][8];
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[j][i] = 0.0f;
+  auto fetch = [&](int r, uint4 (&w)[CHUNKS]) {
+    const __nv_bfloat16* row = base + static_cast<size_t>(tile_channel[r]) * L.H;
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j)
+      w[j] = live[j] ? load_stream16(row + 256 * j) : make_uint4(0, 0, 0, 0);
+  };
+  auto add = [&](int r, const uint4 (&w)[CHUNKS]) {
+    const float a = tile_activation[r];
+#pragma unroll
+    for (int j = 0; j < CHUNKS; ++j) {
+      acc[j][0] = fmaf(bf16_lo(w[j].x), a, acc[j][0]);
+      acc[j][1] = fmaf(bf16_hi(w[j].x), a, acc[j][1]);
+      acc[j][2] = fmaf(bf16_lo(w[j].y), a, acc[j][2]);
+      acc[j][3] = fmaf(bf16_hi(w[j].y), a, acc[j][3]);
+      acc[j][4] = fmaf(bf16_lo(w[j].z), a, acc[j][4]);
+      acc[j][5] = fmaf(bf16_hi(w[j].z), a, acc[j][5]);
+      acc[j][6] = fmaf(bf16_lo(w[j].w), a, acc[j][6]);
+      acc[j][7] = fmaf(bf16_hi(w[j].w), a, acc[j][7]);
+    }
+  };
+  // Three row buffers used in turn: two rows' loads fly while one is added.
+  uint4 first_row[CHUNKS], second_row[CHUNKS], third_row[CHUNKS];
+  if (warp < rows) fetch(warp, first_row);
+  if (warp + 4 < rows) fetch(warp + 4, second_row);
+  for (int r = warp; r < rows; r += 12) {
+    if (r + 8 < rows) fetch(r + 8, third_row);
+    add(r, first_row);
+    if (r + 12 < rows) fetch(r + 12, first_row);
+    if (r + 4 < rows) add(r + 4, second_row);
+    if (r + 16 < rows) fetch(r + 16, second_row);
+    if (r + 8 < rows) add(r + 8, third_row);
+  }
+#pragma unroll
+  for (int j = 0; j < CHUNKS; ++j) {
+    float4* mine = reinterpret_cast<float4*>(&red[warp][256 * j + lane * 8]);
+    mine[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+    mine[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+  }
+  __syncthreads();
+  float* parts = ws.down_parts + (static_cast<size_t>(t) * ws.down_tiles + tile) * L.H +
+                 blockIdx.x * kDownColumns;
+  for (int c = tid * 4; c < kDownColumns; c += 128 * 4) {
+    if (blockIdx.x * kDownColumns + c < L.H) {
+      const float4 a = *reinterpret_cast<const float4*>(&red[0][c]);
+      const float4 b = *reinterpret_cast<const float4*>(&red[1][c]);
+      const float4 d = *reinterpret_cast<const float4*>(&red[2][c]);
+      const float4 g = *reinterpret_cast<const float4*>(&red[3][c]);
+      *reinterpret_cast<float4*>(parts + c) =
+          make_float4(((a.x + b.x) + d.x) + g.x, ((a.y + b.y) + d.y) + g.y,
+                      ((a.z + b.z) + d.z) + g.z, ((a.w + b.w) + d.w) + g.w);
+    }
+  }
+  __syncthreads();  // the shared arrays may be reused
+}
+
 template <bool STRIDED>
 __global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const uint8_t* padding) {
-  constexpr int CHUNKS = kDownColumns / 256;  // 16-byte pieces per lane and row
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
   __shared__ __align__(16) float red[4][kDownColumns];
   __shared__ int s_slot, s_first;
-  const int t = blockIdx.z, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int t = blockIdx.z, tid = threadIdx.x;
   if (padding && padding[t]) return;
   const size_t token_pairs = static_cast<size_t>(t) * L.K;
   int used;
@@ -1586,7 +1738,6 @@ __global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const ui
   }
   int tile = blockIdx.y;
   if (tile >= used) return;
-  const int column0 = blockIdx.x * kDownColumns + lane * 8;  // this lane's first column
   do {
     if (tid == 0) s_slot = -1;
     __syncthreads();
@@ -1603,80 +1754,27 @@ __global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const ui
     __syncthreads();
     const int slot = s_slot, first = s_first;
     if (slot < 0) continue;  // uniform: every thread read the same slot
-    const int e = ws.ids[token_pairs + slot];
-    const int rows = min(kDownTileRows, ws.counts[token_pairs + slot] - first);
-    const int32_t* list =
-        ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first;
-    const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
-    if (tid < rows) {
-      const int cid = list[tid];
-      tile_channel[tid] = cid - slot * L.I;
-      tile_activation[tid] = __bfloat162float(act[cid]);
-    }
-    __syncthreads();
-    const __nv_bfloat16* base = L.down + static_cast<size_t>(e) * L.I * L.H + column0;
-    bool live[CHUNKS];
-#pragma unroll
-    for (int j = 0; j < CHUNKS; ++j) live[j] = column0 + 256 * j < L.H;
-    float acc[CHUNKS][8];
-#pragma unroll
-    for (int j = 0; j < CHUNKS; ++j)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[j][i] = 0.0f;
-    auto fetch = [&](int r, uint4 (&w)[CHUNKS]) {
-      const __nv_bfloat16* row = base + static_cast<size_t>(tile_channel[r]) * L.H;
-#pragma unroll
-      for (int j = 0; j < CHUNKS; ++j)
-        w[j] = live[j] ? load_stream16(row + 256 * j) : make_uint4(0, 0, 0, 0);
-    };
-    auto add = [&](int r, const uint4 (&w)[CHUNKS]) {
-      const float a = tile_activation[r];
-#pragma unroll
-      for (int j = 0; j < CHUNKS; ++j) {
-        acc[j][0] = fmaf(bf16_lo(w[j].x), a, acc[j][0]);
-        acc[j][1] = fmaf(bf16_hi(w[j].x), a, acc[j][1]);
-        acc[j][2] = fmaf(bf16_lo(w[j].y), a, acc[j][2]);
-        acc[j][3] = fmaf(bf16_hi(w[j].y), a, acc[j][3]);
-        acc[j][4] = fmaf(bf16_lo(w[j].z), a, acc[j][4]);
-        acc[j][5] = fmaf(bf16_hi(w[j].z), a, acc[j][5]);
-        acc[j][6] = fmaf(bf16_lo(w[j].w), a, acc[j][6]);
-        acc[j][7] = fmaf(bf16_hi(w[j].w), a, acc[j][7]);
-      }
-    };
-    // Three row buffers used in turn: two rows' loads fly while one is added.
-    uint4 first_row[CHUNKS], second_row[CHUNKS], third_row[CHUNKS];
-    if (warp < rows) fetch(warp, first_row);
-    if (warp + 4 < rows) fetch(warp + 4, second_row);
-    for (int r = warp; r < rows; r += 12) {
-      if (r + 8 < rows) fetch(r + 8, third_row);
-      add(r, first_row);
-      if (r + 12 < rows) fetch(r + 12, first_row);
-      if (r + 4 < rows) add(r + 4, second_row);
-      if (r + 16 < rows) fetch(r + 16, second_row);
-      if (r + 8 < rows) add(r + 8, third_row);
-    }
-#pragma unroll
-    for (int j = 0; j < CHUNKS; ++j) {
-      float4* mine = reinterpret_cast<float4*>(&red[warp][256 * j + lane * 8]);
-      mine[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-      mine[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
-    }
-    __syncthreads();
-    float* parts = ws.down_parts + (static_cast<size_t>(t) * ws.down_tiles + tile) * L.H +
-                   blockIdx.x * kDownColumns;
-    for (int c = tid * 4; c < kDownColumns; c += 128 * 4) {
-      if (blockIdx.x * kDownColumns + c < L.H) {
-        const float4 a = *reinterpret_cast<const float4*>(&red[0][c]);
-        const float4 b = *reinterpret_cast<const float4*>(&red[1][c]);
-        const float4 d = *reinterpret_cast<const float4*>(&red[2][c]);
-        const float4 g = *reinterpret_cast<const float4*>(&red[3][c]);
-        *reinterpret_cast<float4*>(parts + c) =
-            make_float4(((a.x + b.x) + d.x) + g.x, ((a.y + b.y) + d.y) + g.y,
-                        ((a.z + b.z) + d.z) + g.z, ((a.w + b.w) + d.w) + g.w);
-      }
-    }
-    // The barrier at the top of the next tile orders these reads before its writes.
+    down_tile(L, ws, t, slot, first, tile, tile_channel, tile_activation, red);
   } while (STRIDED && (tile += gridDim.y) < used);
+}
+
+// The same tiles with the (token, expert) pairs walked in expert order:
+// grid (ceil(H / 1024), Y, T * K), 128 threads.  CTA layer z takes the z-th pair
+// of the list grouped by expert (k_group); its Y CTAs share the pair's tiles.
+// Tokens of one expert run next to each other in time, so a down row several of
+// them kept comes from HBM once and from L2 after that.  Same tiles, same sums,
+// same bits as k_down.
+__global__ void __launch_bounds__(128, 4) k_down_pairs(Layer L, Workspace ws) {
+  __shared__ int tile_channel[kDownTileRows];
+  __shared__ float tile_activation[kDownTileRows];
+  __shared__ __align__(16) float red[4][kDownColumns];
+  if (static_cast<int>(blockIdx.z) >= ws.group_offsets[L.E]) return;
+  const int pair = ws.group_pairs[blockIdx.z];
+  const int tiles = (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows;
+  const int t = pair / L.K, slot = pair - t * L.K;
+  const int begin = ws.tile_starts[pair];
+  for (int j = blockIdx.y; j < tiles; j += gridDim.y)
+    down_tile(L, ws, t, slot, j * kDownTileRows, begin + j, tile_channel, tile_activation, red);
 }
 
 // ---------------------------------------------------------------------------
@@ -1806,12 +1904,33 @@ __global__ void k_zero_latent(Layer L, Workspace ws) {
     ws.latent[static_cast<size_t>(blockIdx.x) * L.R + r] = 0.0f;
 }
 
+#include "cfm_grouped.cuh"
+
+// One past the last down tile of slot `slot` of token t.  The per-token down
+// kernel lays a token's tiles out slot after slot, ceil(count / 64) tiles per
+// local slot, starting at `tile_starts`; the expert-major one writes `fixed`
+// partial sums for every local slot, slot after slot.
+__device__ __forceinline__ int down_slot_end(const Layer& L, const Workspace& ws, int t, int slot,
+                                             int fixed) {
+  const size_t pairs = static_cast<size_t>(t) * L.K;
+  if (fixed == 0) {
+    const int tiles = ws.ids[pairs + slot] >= 0
+                          ? (ws.counts[pairs + slot] + kDownTileRows - 1) / kDownTileRows : 0;
+    return ws.tile_starts[pairs + slot] + tiles;
+  }
+  int local = 0;
+  for (int s = 0; s <= slot; ++s) local += ws.ids[pairs + s] >= 0;
+  return local * fixed;
+}
+
 // ---------------------------------------------------------------------------
 // output: router mix + decoder term
 // ---------------------------------------------------------------------------
-// grid (H / 128, T), 128 threads, one output column per thread.
+// grid (H / 128, T), 128 threads, one output column per thread.  `fixed` is the
+// number of partial sums per local slot the expert-major down kernel wrote, or 0
+// after the per-token down kernel.
 __global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uint8_t* padding,
-                                                __nv_bfloat16* out) {
+                                                __nv_bfloat16* out, int fixed) {
   __shared__ float latent[256];
   __shared__ int slot_end[32];       // one past the last down tile of every slot
   __shared__ float slot_weight[32];
@@ -1823,9 +1942,7 @@ __global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uin
   const bool recover = L.R > 0 && L.owner && L.decoder;
   if (tid < L.K) {
     const size_t pair = static_cast<size_t>(t) * L.K + tid;
-    const int tiles =
-        ws.ids[pair] >= 0 ? (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows : 0;
-    slot_end[tid] = ws.tile_starts[pair] + tiles;
+    slot_end[tid] = down_slot_end(L, ws, t, tid, fixed);
     slot_weight[tid] = ws.weights[pair];
   }
   if (recover)
@@ -1888,13 +2005,50 @@ __global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uin
 // BF16-rounded expert sums, no decoder term.  k_finish runs on the token's home
 // rank after the partial sums and latents of all ranks have been added: decoder
 // term and BF16 store.  grid (H / 128, T), 128 threads each.
+// With `peers` row t goes straight into slot [this rank] of the `rows` of its home
+// rank's exchange block (no latent: the home rank computes its own), and the last
+// CTA of a home rank's rows announces the epoch there.
 __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
-                                                        const uint8_t* padding, float* combined) {
+                                                        const uint8_t* padding, float* combined,
+                                                        int fixed, Exchange x, int peers) {
   __shared__ int slot_end[32];
   __shared__ float slot_weight[32];
   const int t = blockIdx.y, tid = threadIdx.x, h = blockIdx.x * 128 + tid;
   float* routed_out = combined + static_cast<size_t>(t) * (L.H + L.R);
   const bool padded = padding && padding[t];
+  if (peers) {
+    const int home = t / x.tokens, row = t - home * x.tokens;
+    routed_out = reinterpret_cast<float*>(x.block[home] +
+                                          exchange_rows_offset(x.world, x.tokens, L.F)) +
+                 (static_cast<size_t>(x.rank) * x.tokens + row) * L.H;
+    float routed = 0.0f;
+    if (!padded) {
+      if (tid < L.K) {
+        slot_end[tid] = down_slot_end(L, ws, t, tid, fixed);
+        slot_weight[tid] = ws.weights[static_cast<size_t>(t) * L.K + tid];
+      }
+      __syncthreads();
+      const int used = slot_end[L.K - 1];
+      const float* parts = ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h;
+      float sum = 0.0f;
+      int slot = 0;
+      for (int tile = 0; tile < used; ++tile) {
+        while (tile >= slot_end[slot]) {
+          routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+          sum = 0.0f;
+          ++slot;
+        }
+        sum += parts[static_cast<size_t>(tile) * L.H];
+      }
+      if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+    }
+    routed_out[h] = routed;
+    uint32_t* header = exchange_header(x, x.rank);
+    exchange_announce(header + kExchangeRowsArrive + home, gridDim.x * x.tokens,
+                      exchange_header(x, home) + kExchangeRowsFlag + x.rank,
+                      header[kExchangeEpoch] + 1u);
+    return;
+  }
   if (blockIdx.x == 0)  // this rank's share of the latent rides behind the H outputs
     for (int r = tid; r < L.R; r += 128)
       routed_out[L.H + r] = padded ? 0.0f : ws.latent[static_cast<size_t>(t) * L.R + r];
@@ -1904,9 +2058,7 @@ __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
   }
   if (tid < L.K) {
     const size_t pair = static_cast<size_t>(t) * L.K + tid;
-    const int tiles =
-        ws.ids[pair] >= 0 ? (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows : 0;
-    slot_end[tid] = ws.tile_starts[pair] + tiles;
+    slot_end[tid] = down_slot_end(L, ws, t, tid, fixed);
     slot_weight[tid] = ws.weights[pair];
   }
   __syncthreads();
@@ -1983,6 +2135,8 @@ static int bind_call(const cfm_layer* layer, void* workspace, int32_t capacity,
   if (layer->activation != CFM_ACT_SILU && layer->activation != CFM_ACT_GELU_TANH)
     return CFM_E_UNSUPPORTED;
   if (layer->score != CFM_SCORE_POINT && layer->score != CFM_SCORE_RECOVERY_AWARE)
+    return CFM_E_UNSUPPORTED;
+  if (layer->row_engine < CFM_ROWS_AUTO || layer->row_engine > CFM_ROWS_EXPERT_MAJOR)
     return CFM_E_UNSUPPORTED;
   const bool screened = layer->final_count < layer->top_k * layer->width;
   if (screened && (!layer->sketch || !layer->statistics || !layer->norms || !layer->signs))
@@ -2119,13 +2273,67 @@ static int run_score(const Bound& b) {
   return launched();
 }
 
-static int run_exact(const Bound& b, const cfm_call* call) {
-  if (!call->hidden || !b.L.gate_up) return CFM_E_NULL;
-  const size_t smem = static_cast<size_t>(b.L.H) * 2;
+// Batches whose pairs are grouped by expert also read the experts' native rows
+// expert-major (the groups come from k_group, launched by route and adopt).
+static bool pairs_grouped(const Bound& b) { return screens_grouped(b); }
+
+// Expert-major exact, down and encode: a row is read once for all the tokens of
+// its expert that kept it.  Pays from about eight tokens per expert, where the
+// union of their kept channels is well below their sum; below that the per-token
+// kernels run, walking the pairs in expert order.
+static bool rows_grouped(const Bound& b) {
+  if (!pairs_grouped(b) || b.L.row_engine == CFM_ROWS_PER_TOKEN) return false;
+  if (b.L.row_engine == CFM_ROWS_EXPERT_MAJOR) return true;
+  return static_cast<int64_t>(b.T) * b.L.K >= 8 * static_cast<int64_t>(b.L.E);
+}
+
+// Partial sums per (token, local slot) of the expert-major down kernel: enough
+// CTAs to fill the device, at most what the workspace has room for.
+static int down_grouped_parts(const Bound& b) {
+  const int64_t column_blocks = (b.L.H + kDownGroupedColumns - 1) / kDownGroupedColumns;
+  const int64_t wanted = (8 * 148 + column_blocks * b.L.E - 1) / (column_blocks * b.L.E);
+  const int64_t room = std::min<int64_t>(kDownGroupedMaxParts, b.ws.down_tiles / b.L.K);
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::max<int64_t>(2, wanted), room)));
+}
+
+static int run_exact_grouped(const Bound& b, const cfm_call* call) {
+  // Entries of the per-channel token table: four times the mean number of kept
+  // channels per expert, at least one expert's width (the largest one token can need).
+  const int64_t mean = (static_cast<int64_t>(b.T) * b.L.F + b.L.E - 1) / b.L.E;
+  const int entries = static_cast<int>(
+      std::min<int64_t>(16384, std::max<int64_t>(b.L.I, 4 * mean)));
+  const size_t smem = exact_grouped_bytes(b.L.I, entries);
   if (smem > 48 * 1024) {
     const cudaError_t err = cudaFuncSetAttribute(
-        k_exact, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        k_exact_grouped, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  const int parts = static_cast<int>(
+      std::max<int64_t>(1, std::min<int64_t>(32, (4 * 148 + b.L.E - 1) / b.L.E)));
+  k_exact_grouped<<<dim3(parts, b.L.E), kExactGroupedThreads, smem, b.stream>>>(
+      b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden), entries);
+  return launched();
+}
+
+static int run_exact(const Bound& b, const cfm_call* call) {
+  if (!call->hidden || !b.L.gate_up) return CFM_E_NULL;
+  if (rows_grouped(b)) return run_exact_grouped(b, call);
+  const size_t smem = static_cast<size_t>(b.L.H) * 2;
+  if (smem > 48 * 1024) {
+    cudaError_t err = cudaFuncSetAttribute(
+        k_exact, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(k_exact_pairs, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+    if (err != cudaSuccess) return static_cast<int>(err);
+  }
+  if (pairs_grouped(b)) {
+    // One warp per kept row of a pair when the pair keeps the mean number of rows.
+    const int per_pair = (b.L.F + b.L.K - 1) / b.L.K;
+    const int ctas = std::max(1, (per_pair + kExactWarps - 1) / kExactWarps);
+    k_exact_pairs<<<dim3(ctas, b.T * b.L.K), kExactWarps * 32, smem, b.stream>>>(
+        b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden));
+    return launched();
   }
   int ctas = (b.L.F + kExactWarps - 1) / kExactWarps;
   if (b.L.expert_map && b.L.global_experts > 0) {
@@ -2142,6 +2350,26 @@ static int run_exact(const Bound& b, const cfm_call* call) {
 
 static int run_down(const Bound& b) {
   if (!b.L.down) return CFM_E_NULL;
+  if (rows_grouped(b)) {
+    const size_t smem = down_grouped_bytes(b.L.I);
+    if (smem > 48 * 1024) {
+      const cudaError_t err = cudaFuncSetAttribute(
+          k_down_grouped, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (err != cudaSuccess) return static_cast<int>(err);
+    }
+    const int parts = down_grouped_parts(b);
+    const dim3 grid((b.L.H + kDownGroupedColumns - 1) / kDownGroupedColumns, b.L.E, parts);
+    k_down_grouped<<<grid, kDownGroupedThreads, smem, b.stream>>>(b.L, b.ws, parts);
+    return launched();
+  }
+  if (pairs_grouped(b)) {
+    // Tiles per pair at the mean number of kept rows, one more for the busy slots.
+    const int per_pair = (b.L.F + b.L.K - 1) / b.L.K;
+    const int share = (per_pair + kDownTileRows - 1) / kDownTileRows + 1;
+    const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, share, b.T * b.L.K);
+    k_down_pairs<<<grid, 128, 0, b.stream>>>(b.L, b.ws);
+    return launched();
+  }
   int tiles = b.ws.down_tiles;
   if (b.L.expert_map && b.L.global_experts > 0) {
     // Expert parallel: about E / global of a token's tiles are local; twice that
@@ -2163,6 +2391,16 @@ static int run_encode(const Bound& b) {
     k_zero_latent<<<b.T, 128, 0, b.stream>>>(b.L, b.ws);
     return launched();
   }
+  if (rows_grouped(b) && !b.L.expert_map) {
+    const size_t smem = encode_grouped_bytes(b.L.R);
+    if (smem > 48 * 1024) {
+      const cudaError_t err = cudaFuncSetAttribute(
+          k_encode_grouped, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      if (err != cudaSuccess) return static_cast<int>(err);
+    }
+    k_encode_grouped<<<dim3(b.ws.encoder_tiles, b.L.E), kEncodeThreads, smem, b.stream>>>(b.L, b.ws);
+    return launched();
+  }
   k_encode<<<dim3(b.ws.encoder_tiles, b.T * b.L.K), kEncodeThreads, 0, b.stream>>>(b.L, b.ws, b.padding);
   return launched();
 }
@@ -2170,7 +2408,8 @@ static int run_encode(const Bound& b) {
 static int run_output(const Bound& b, const cfm_call* call) {
   if (!call->out) return CFM_E_NULL;
   k_output<<<dim3(b.L.H / 128, b.T), 128, 0, b.stream>>>(
-      b.L, b.ws, b.padding, static_cast<__nv_bfloat16*>(call->out));
+      b.L, b.ws, b.padding, static_cast<__nv_bfloat16*>(call->out),
+      rows_grouped(b) ? down_grouped_parts(b) : 0);
   return launched();
 }
 
@@ -2207,6 +2446,24 @@ static int side_stream(SideStream* out) {
     slot.ready = true;
   }
   *out = slot;
+  return 0;
+}
+
+// Checks an exchange description against the layer and the call (`rows` = tokens
+// of all ranks) and makes the device-visible copy.
+static int bind_exchange(const cfm_exchange* e, const cfm_layer* layer, int rows, Exchange* out) {
+  if (!e || !layer) return CFM_E_NULL;
+  if (e->world < 1 || e->world > CFM_MAX_RANKS || e->rank < 0 || e->rank >= e->world ||
+      e->tokens < 1)
+    return CFM_E_SHAPE;
+  if (rows != e->world * e->tokens) return CFM_E_CAPACITY;
+  out->world = e->world;
+  out->rank = e->rank;
+  out->tokens = e->tokens;
+  for (int p = 0; p < CFM_MAX_RANKS; ++p) {
+    out->block[p] = p < e->world ? static_cast<char*>(e->blocks[p]) : nullptr;
+    if (p < e->world && !e->blocks[p]) return CFM_E_NULL;
+  }
   return 0;
 }
 
@@ -2262,9 +2519,17 @@ int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity
   Bound b;
   const int rc = bind_call(layer, workspace, capacity, call, stream, &b);
   if (rc) return rc;
-  if (!call->out) return CFM_E_NULL;
+  Exchange x = {};
+  const int peers = call->exchange != nullptr;
+  if (peers) {
+    const int code = bind_exchange(call->exchange, layer, b.T, &x);
+    if (code) return code;
+  } else if (!call->out) {
+    return CFM_E_NULL;
+  }
   k_partial_output<<<dim3(b.L.H / 128, b.T), 128, 0, b.stream>>>(
-      b.L, b.ws, b.padding, static_cast<float*>(call->out));
+      b.L, b.ws, b.padding, static_cast<float*>(call->out),
+      rows_grouped(b) ? down_grouped_parts(b) : 0, x, peers);
   return launched();
 }
 
@@ -2286,9 +2551,95 @@ int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const c
   Bound b;
   const int rc = bind_call(layer, workspace, capacity, call, stream, &b);
   if (rc) return rc;
-  if (!call->ids || !call->weights || !call->lists) return CFM_E_NULL;
+  if (!call->ids || !call->weights || (!call->lists && !call->exchange)) return CFM_E_NULL;
+  Exchange x = {};
+  const int peers = call->exchange != nullptr;
+  if (peers) {
+    const int bound = bind_exchange(call->exchange, layer, b.T, &x);
+    if (bound) return bound;
+  }
   k_adopt<<<b.T, 256, 0, b.stream>>>(b.L, b.ws, call->ids, call->ids_are_int64, call->weights,
-                                     call->weights_are_bf16, b.padding, call->lists);
+                                     call->weights_are_bf16, b.padding, call->lists, x, peers);
+  int code = launched();
+  if (code || !pairs_grouped(b)) return code;
+  // The exact and down kernels read the pairs grouped by expert.
+  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
+  return launched();
+}
+
+int64_t cfm_exchange_bytes(const cfm_layer* layer, int32_t world, int32_t tokens) {
+  if (!layer || world < 1 || world > CFM_MAX_RANKS || tokens < 1) return 0;
+  return static_cast<int64_t>(
+      exchange_bytes(world, tokens, layer->final_count, layer->hidden));
+}
+
+int cfm_peer_alloc(int64_t bytes, void** block) {
+  if (!block || bytes < 1) return CFM_E_NULL;
+  cudaError_t err = cudaMalloc(block, static_cast<size_t>(bytes));
+  if (err == cudaSuccess) err = cudaMemset(*block, 0, static_cast<size_t>(bytes));
+  if (err == cudaSuccess) err = cudaDeviceSynchronize();
+  return static_cast<int>(err);
+}
+
+int cfm_peer_export(void* block, void* handle) {
+  if (!block || !handle) return CFM_E_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == CFM_PEER_HANDLE_BYTES, "handle size");
+  return static_cast<int>(
+      cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle), block));
+}
+
+int cfm_peer_import(const void* handle, void** block) {
+  if (!block || !handle) return CFM_E_NULL;
+  cudaIpcMemHandle_t copy;
+  memcpy(&copy, handle, sizeof(copy));
+  return static_cast<int>(cudaIpcOpenMemHandle(block, copy, cudaIpcMemLazyEnablePeerAccess));
+}
+
+int cfm_peer_release(void* block, int32_t imported) {
+  if (!block) return 0;
+  return static_cast<int>(imported ? cudaIpcCloseMemHandle(block) : cudaFree(block));
+}
+
+int cfm_exchange_status(const cfm_exchange* exchange, int32_t* status) {
+  if (!exchange || !status || exchange->rank < 0 || exchange->rank >= CFM_MAX_RANKS ||
+      !exchange->blocks[exchange->rank])
+    return CFM_E_NULL;
+  uint32_t word = 0;
+  const cudaError_t err = cudaMemcpy(
+      &word, static_cast<const uint32_t*>(exchange->blocks[exchange->rank]) + kExchangeStatus,
+      sizeof(word), cudaMemcpyDeviceToHost);
+  *status = static_cast<int32_t>(word);
+  return static_cast<int>(err);
+}
+
+int cfm_exchange_send_lists(const cfm_layer* layer, void* workspace, int32_t capacity,
+                            const cfm_call* call, void* stream) {
+  Bound b;
+  const int rc = bind_call(layer, workspace, capacity, call, stream, &b);
+  if (rc) return rc;
+  if (!call->exchange) return CFM_E_NULL;
+  Exchange x = {};
+  const int bound = bind_exchange(call->exchange, layer, call->exchange->world * b.T, &x);
+  if (bound) return bound;
+  if (b.T != x.tokens) return CFM_E_CAPACITY;
+  const int64_t pieces = (static_cast<int64_t>(b.T) * b.L.F + 1023) / 1024;
+  const int ctas = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(32, pieces)));
+  k_send_lists<<<dim3(x.world, ctas), 256, 0, b.stream>>>(b.L, b.ws, x);
+  return launched();
+}
+
+int cfm_finish_rows(const cfm_layer* layer, const cfm_exchange* exchange, const float* latent,
+                    void* out, void* stream) {
+  if (!layer || !exchange || !out) return CFM_E_NULL;
+  cfm_workspace_layout layout;
+  const int rc = make_layout(layer, 1, &layout);  // validates the dimensions
+  if (rc) return rc;
+  Exchange x = {};
+  const int bound = bind_exchange(exchange, layer, exchange->world * exchange->tokens, &x);
+  if (bound) return bound;
+  const Layer L = device_layer(layer);
+  k_finish_rows<<<dim3(L.H / 128, x.tokens), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      L, x, latent, static_cast<__nv_bfloat16*>(out));
   return launched();
 }
 

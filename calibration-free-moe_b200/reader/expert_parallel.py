@@ -49,6 +49,16 @@ before its single BF16 rounding.  The kept channels are the same bit for bit.
 The collectives are plain `torch.distributed` calls on tensors, so the same
 orchestration runs over NCCL with the CUDA engines and over gloo with CPU
 engines in the tests.
+
+Exchange over peer memory (`exchange="peer"`, the default on NCCL groups of one
+box).  With the replicated screen the two exchanges on the critical path, the kept
+lists out and the partial rows back, need no collective: every rank maps a block
+of every other rank's device memory (CUDA IPC), the selection's lists are stored
+straight into all ranks' blocks by a kernel of the library, the owners' partial
+rows straight into the home rank's block, and the kernels that consume them wait
+on a flag the last storing CTA sets.  The home rank adds the owners' rows in rank
+order, so its sum no longer depends on the order of a reduction tree.  Hidden
+rows and router outputs still travel by `all_gather`, started before the screen.
 """
 
 from __future__ import annotations
@@ -174,13 +184,17 @@ def replicated_screen_forward(
     if padding is not None:
         pending.append(_start_gather_rows(padding.view(torch.uint8), world, group))
     lists = engine.choose(hidden, ids, weights, padding)
-    pending.append(_start_gather_rows(lists, world, group))
+    peers = getattr(engine, "exchange", None) is not None
+    if not peers:  # over peer memory `choose` has already stored the lists everywhere
+        pending.append(_start_gather_rows(lists, world, group))
     for _, work in pending:
         work.wait()
     all_hidden, all_ids, all_weights = (gathered for gathered, _ in pending[:3])
     all_padding = pending[3][0].view(torch.bool) if padding is not None else None
-    all_lists = pending[-1][0]
+    all_lists = None if peers else pending[-1][0]
     routed = engine.serve(all_hidden, all_ids, all_weights, all_padding, all_lists)
+    if peers:  # the rows are already in the home ranks' blocks
+        return engine.finish(None)
     mine = _reduce_scatter_in_place(routed, world, rank, group)
     return engine.finish(mine)
 
@@ -208,6 +222,58 @@ def expert_parallel_forward(
     combined = engine.local()
     mine = _reduce_scatter_in_place(combined, world, rank, group)
     return engine.finish(mine)
+
+
+class PeerExchange:
+    """One rank's exchange block and its view of the other ranks' blocks (CUDA IPC).
+
+    Every rank allocates a block of `cfm_exchange_bytes` bytes with the library,
+    publishes its IPC handle through the process group and opens the others'.
+    The ranks must share one box with peer access between their GPUs; if a rank
+    cannot open a block, all ranks report failure (`available` False) and the
+    caller falls back to the collectives.  Blocks live until the process exits.
+    """
+
+    def __init__(self, layer: "_native.Layer", tokens: int, group) -> None:
+        library = _native.load()
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.world, self.rank, self.tokens = world, rank, tokens
+        self.struct = _native.Exchange()
+        self.struct.world, self.struct.rank, self.struct.tokens = world, rank, tokens
+        self.available = False
+        if world > _native.MAX_RANKS:
+            return
+        size = library.cfm_exchange_bytes(ctypes.byref(layer), world, tokens)
+        block = ctypes.c_void_p()
+        good = size > 0 and library.cfm_peer_alloc(size, ctypes.byref(block)) == 0
+        handle = (ctypes.c_ubyte * _native.PEER_HANDLE_BYTES)()
+        good = good and library.cfm_peer_export(block, handle) == 0
+        handles: list = [None] * world
+        dist.all_gather_object(handles, bytes(handle) if good else None, group=group)
+        self.bytes = int(size)
+        if good and all(h is not None for h in handles):
+            for peer in range(world):
+                if peer == rank:
+                    self.struct.blocks[peer] = block.value
+                    continue
+                opened = ctypes.c_void_p()
+                raw = (ctypes.c_ubyte * _native.PEER_HANDLE_BYTES).from_buffer_copy(handles[peer])
+                if library.cfm_peer_import(raw, ctypes.byref(opened)) != 0:
+                    good = False
+                    break
+                self.struct.blocks[peer] = opened.value
+        else:
+            good = False
+        verdicts: list = [None] * world
+        dist.all_gather_object(verdicts, bool(good), group=group)  # also: everyone has opened
+        self.available = all(verdicts)
+
+    def status(self) -> int:
+        """Bits of the waits that ran out since the block was made (synchronises)."""
+        word = ctypes.c_int32()
+        code = _native.load().cfm_exchange_status(ctypes.byref(self.struct), ctypes.byref(word))
+        _native.check(code, "cfm_exchange_status")
+        return int(word.value)
 
 
 class ShardedScreenEngine:
@@ -343,8 +409,10 @@ class _HomeScreen:
 class ReplicatedScreenEngine:
     """The CUDA library as the replicated-screen back end of one rank."""
 
-    def __init__(self, owner: ProgressiveReader, home: _HomeScreen, max_tokens: int) -> None:
+    def __init__(self, owner: ProgressiveReader, home: _HomeScreen, max_tokens: int,
+                 exchange: PeerExchange | None = None) -> None:
         self.owner, self.home, self.max_tokens = owner, home, max_tokens
+        self.exchange = exchange
         device = owner._device
         self._routed = torch.empty(owner.max_tokens, owner.plan.hidden_size, device=device,
                                    dtype=torch.float32)
@@ -378,6 +446,12 @@ class ReplicatedScreenEngine:
             if screened:
                 self._home_stage("cfm_screen", call)
             self._home_stage("cfm_select", call)
+            if self.exchange is not None:
+                if rows != self.exchange.tokens:
+                    raise ValueError("The peer-memory exchange needs the full batch on every rank "
+                                     "(use `padding` for ragged batches)")
+                call.exchange = ctypes.addressof(self.exchange.struct)
+                self._home_stage("cfm_exchange_send_lists", call)
             if home.rank:
                 main = torch.cuda.current_stream(device)
                 self._fork.record(main)
@@ -392,7 +466,10 @@ class ReplicatedScreenEngine:
         owner = self.owner
         rows = owner._validate_input(hidden, padding)
         call = owner._call_struct(rows, hidden, ids, weights, padding, self._routed, False)
-        call.lists = lists.data_ptr()
+        if self.exchange is not None:
+            call.exchange = ctypes.addressof(self.exchange.struct)
+        else:
+            call.lists = lists.data_ptr()
         self._serve_keep = (hidden, ids, weights, padding, lists)
         with torch.cuda.device(owner._device):
             for stage in ("cfm_adopt", "cfm_exact", "cfm_down", "cfm_partial_output"):
@@ -401,12 +478,20 @@ class ReplicatedScreenEngine:
 
     def finish(self, routed):
         home, device = self.home, self.owner._device
-        rows = routed.shape[0]
+        rows = routed.shape[0] if routed is not None else self._rows
         out = torch.empty((rows, self.owner.plan.hidden_size), device=device, dtype=torch.bfloat16)
         with torch.cuda.device(device):
             main = torch.cuda.current_stream(device)
             if home.rank:
                 main.wait_event(self._join)
+            if routed is None:  # the owners stored their rows into this rank's exchange block
+                code = self._library.cfm_finish_rows(
+                    ctypes.byref(home.layer), ctypes.byref(self.exchange.struct),
+                    home.workspace.latent.data_ptr() if home.rank else None, out.data_ptr(),
+                    ctypes.c_void_p(main.cuda_stream),
+                )
+                _native.check(code, "cfm_finish_rows")
+                return out
             code = self._library.cfm_finish(
                 ctypes.byref(home.layer), rows, routed.data_ptr(),
                 home.workspace.latent.data_ptr() if home.rank else None, out.data_ptr(),
@@ -427,7 +512,12 @@ class ExpertParallelReader:
     `screen` picks the strategy: "replicated" (default; every rank also keeps
     the sketch, norms and recovery encoder of all experts and screens its own
     tokens alone) or "sharded" (nothing but the decoder is replicated; ranks
-    exchange scores).  Both keep the same channels.
+    exchange scores).  Both keep the same channels.  `exchange` picks how the
+    replicated screen moves the kept lists and the partial rows: "peer" (kernels
+    of the library over memory the ranks map from each other; every call must
+    then bring exactly `max_tokens` rows), "collective" (`all_gather` and
+    `reduce_scatter`) or "auto" (peer memory when the group runs over NCCL and
+    the mapping works).
     """
 
     def __init__(
@@ -442,15 +532,19 @@ class ExpertParallelReader:
         global_experts: int,
         group=None,
         screen: str = "replicated",
+        exchange: str = "auto",
         **reader_options,
     ) -> None:
         if screen not in ("replicated", "sharded"):
             raise ValueError("screen must be 'replicated' or 'sharded'")
+        if exchange not in ("auto", "peer", "collective"):
+            raise ValueError("exchange must be 'auto', 'peer' or 'collective'")
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         if gate_up.shape[0] * self.world != global_experts:
             raise ValueError("Local experts times ranks must equal the global expert count")
         self.max_tokens, self.screen = max_tokens, screen
+        self.exchange: PeerExchange | None = None
         expert_map = linear_expert_map(global_experts, self.world, self.rank)
         if screen == "sharded":
             self.reader = ProgressiveReader(
@@ -482,7 +576,18 @@ class ExpertParallelReader:
         local.sketch_statistics = home.sketch_statistics[span].permute(0, 3, 1, 2)
         local._layer.statistics = local.sketch_statistics.data_ptr()
         local.sketch_resident_bytes = 0
-        self.engine = ReplicatedScreenEngine(self.reader, self.home, max_tokens)
+        # Lists and partial rows over peer memory where the ranks can map each other's
+        # memory; "peer" insists on it, "auto" falls back to the collectives.
+        peer = None
+        on_nccl = gate_up.is_cuda and dist.get_backend(self.group) == "nccl"
+        if exchange != "collective" and on_nccl:
+            peer = PeerExchange(self.home.layer, max_tokens, self.group)
+            if not peer.available:
+                peer = None
+        if exchange == "peer" and peer is None:
+            raise RuntimeError("The ranks cannot map each other's device memory (CUDA IPC)")
+        self.exchange = peer
+        self.engine = ReplicatedScreenEngine(self.reader, self.home, max_tokens, peer)
 
     @torch.no_grad()
     def __call__(self, hidden: Tensor, ids: Tensor, weights: Tensor,

@@ -29,6 +29,7 @@ from .budget import sketch_storage_bytes
 SelectionScore = Literal["recovery-aware", "point"]
 SCORE_CODES = {"point": 0, "recovery-aware": 1}
 TENSOR_ENGINES = {"mma_sync": 0, "tcgen05": 1}
+ROW_ENGINES = {"auto": 0, "per_token": 1, "expert_major": 2}
 
 # Accepted for interface compatibility; this implementation has one execution
 # path whose results do not depend on them.
@@ -224,6 +225,7 @@ class ProgressiveReader:
         recovery_owner: bool | None = None,
         retain_reference_sketch: bool = True,
         tensor_engine: str = "mma_sync",
+        row_engine: str = "auto",
     ) -> None:
         """Prepare the sketch, norms and workspace of one layer.
 
@@ -243,7 +245,13 @@ class ProgressiveReader:
         of the group) and `retain_reference_sketch` (keep the reference-layout
         codes resident beside the kernel layout) and `tensor_engine`, the
         tensor-core path of the expert-major screen: "mma_sync" (default, measured
-        faster) or "tcgen05" (tensor-memory accumulators); both give the same bits.
+        faster) or "tcgen05" (tensor-memory accumulators); both give the same bits;
+        and `row_engine`, how batches of eight tokens and more read the native
+        rows: "expert_major" (a row several tokens of one expert kept is read once
+        for all of them), "per_token" (one gather per token, tokens of one expert
+        next to each other in time so that shared rows meet in L2) or "auto"
+        (expert-major from eight tokens per expert on average).  The kept channels
+        do not depend on it; outputs differ by FP32 summation order only.
 
         Contract violations raise ValueError before anything is launched.
         """
@@ -263,6 +271,8 @@ class ProgressiveReader:
             raise ValueError("selection_score must be 'recovery-aware' or 'point'")
         if tensor_engine not in TENSOR_ENGINES:
             raise ValueError("tensor_engine must be 'mma_sync' or 'tcgen05'")
+        if row_engine not in ROW_ENGINES:
+            raise ValueError("row_engine must be 'auto', 'per_token' or 'expert_major'")
         if activation not in ACTIVATION_CODES:
             raise ValueError(f"Unsupported routed expert activation: {activation}")
         if screen_block_splits not in (1, 2, 4, 8) or grouped_screen_splits not in (1, 2, 4, 8):
@@ -419,6 +429,7 @@ class ProgressiveReader:
         layer.activation = ACTIVATION_CODES[activation]
         layer.score = SCORE_CODES[selection_score]
         layer.tensor_engine = TENSOR_ENGINES[tensor_engine]
+        layer.row_engine = ROW_ENGINES[row_engine]
         layer.global_experts = self.expert_map.numel() if self.expert_map is not None else 0
         layer.recovery_owner = int(self.recovery_owner)
         layer.gate_up = self.native_gu.data_ptr()

@@ -43,6 +43,9 @@ extern "C" {
 #define CFM_SCORE_RECOVERY_AWARE 1
 #define CFM_ENGINE_MMA_SYNC 0 /* warp-level mma.sync.m16n8k32 (default: measured faster) */
 #define CFM_ENGINE_TCGEN05 1  /* tcgen05.mma kind::i8, accumulators in tensor memory     */
+#define CFM_ROWS_AUTO 0        /* expert-major from eight tokens per expert on average */
+#define CFM_ROWS_PER_TOKEN 1   /* native rows always gathered per token                 */
+#define CFM_ROWS_EXPERT_MAJOR 2 /* expert-major whenever the pairs are grouped (T >= 8) */
 #define CFM_READ_WORK_SLOTS 20
 
 /* One MoE layer: dimensions and resident tensors.  Mirrors the state
@@ -60,6 +63,8 @@ typedef struct cfm_layer {
   int32_t global_experts; /* length of expert_map, 0 when expert_map is NULL   */
   int32_t recovery_owner; /* 1 if this rank adds the decoder term              */
   int32_t tensor_engine;  /* CFM_ENGINE_*: tensor-core path of the grouped screen */
+  int32_t row_engine;     /* CFM_ROWS_*: how exact, down and encode walk the native rows */
+  int32_t reserved;
   const void* gate_up;       /* bf16 [E, 2I, H] contiguous                      */
   const void* down;          /* bf16 physical [E, I, H] (channel-major)         */
   const uint32_t* sketch;    /* coordinate-major layout [E, H, 2I/16], 2 bits per trit */
@@ -75,6 +80,21 @@ typedef struct cfm_layer {
   const float* selection_threshold; /* device f32 scalar: keep scores >= it, at most F
                                        per token; NULL = plain top-F                 */
 } cfm_layer;
+
+/* Expert parallelism over peer memory: every rank of the box owns one exchange
+ * block of cfm_exchange_bytes() bytes in its own device memory, and all ranks have
+ * mapped all blocks (cfm_peer_alloc / cfm_peer_export / cfm_peer_import, CUDA IPC).
+ * `blocks[p]` is rank p's block as this process sees it.  One layer call is one
+ * epoch of the exchange; all ranks must make the same sequence of calls. */
+#define CFM_MAX_RANKS 16
+#define CFM_PEER_HANDLE_BYTES 64
+typedef struct cfm_exchange {
+  int32_t world;          /* P, ranks of the box sharing the experts            */
+  int32_t rank;           /* this rank                                          */
+  int32_t tokens;         /* T, tokens every rank brings per call (fixed)       */
+  int32_t reserved;
+  void* blocks[CFM_MAX_RANKS];
+} cfm_exchange;
 
 /* One call.  Mirrors the arguments of `ProgressiveReader.__call__`
  * (reference progressive.py:3875-3926). */
@@ -96,6 +116,11 @@ typedef struct cfm_call {
   const int32_t* lists;   /* cfm_adopt only: i32 [T, F] kept candidate ids chosen
                              by the tokens' home ranks, ascending, -1 after the
                              last; NULL elsewhere                               */
+  const struct cfm_exchange* exchange; /* expert parallelism over peer memory, or NULL:
+                             cfm_adopt then reads the lists the home ranks stored
+                             into this rank's exchange block and
+                             cfm_partial_output stores its rows into the home
+                             ranks' blocks (see cfm_exchange below)              */
 } cfm_call;
 
 /* Byte offsets of every scratch array inside one workspace allocation of
@@ -243,6 +268,33 @@ int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined,
  * the scores instead (progressive.py:4245-4251). */
 int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const cfm_call* call,
               void* stream);
+
+/* Expert parallelism over peer memory (NVLink), replacing the collectives around
+ * cfm_adopt and cfm_partial_output.  Per layer call and rank: cfm_exchange_send_lists
+ * (home side, after cfm_select) stores the kept lists of this rank's T tokens into
+ * every rank's block; cfm_adopt with call->exchange waits for the lists of each
+ * row's home rank; cfm_partial_output with call->exchange stores each row's FP32
+ * partial sums into the block of the row's home rank; cfm_finish_rows (home side)
+ * waits for the rows of all ranks, adds them in rank order, adds the decoder term
+ * of `latent` (f32 [T, R], or NULL) and stores BF16 `out` [T, H].  Every device-side
+ * wait is bounded (about a second); a wait that ran out sets a bit in the status
+ * word cfm_exchange_status reads (1: lists, 2: rows; the call synchronises) and
+ * the results of that call are not to be trusted.  No reference counterpart: the
+ * reference replicates the tokens and all-reduces (progressive.py:4245-4251,
+ * 4444-4445).  cfm_peer_alloc allocates (and zeroes) a block with cudaMalloc;
+ * cfm_peer_export writes its CFM_PEER_HANDLE_BYTES-byte IPC handle, which
+ * cfm_peer_import opens in another process of the same box; these four are set-up
+ * calls and synchronise. */
+int64_t cfm_exchange_bytes(const cfm_layer* layer, int32_t world, int32_t tokens);
+int cfm_peer_alloc(int64_t bytes, void** block);
+int cfm_peer_export(void* block, void* handle);
+int cfm_peer_import(const void* handle, void** block);
+int cfm_peer_release(void* block, int32_t imported);
+int cfm_exchange_status(const cfm_exchange* exchange, int32_t* status);
+int cfm_exchange_send_lists(const cfm_layer* layer, void* workspace, int32_t capacity,
+                            const cfm_call* call, void* stream);
+int cfm_finish_rows(const cfm_layer* layer, const cfm_exchange* exchange, const float* latent,
+                    void* out, void* stream);
 
 /* The whole layer on one stream: prepare (unless input_prepared), route,
  * screen, select, exact, down, encode, output.  Single-device readers only;

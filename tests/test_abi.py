@@ -27,7 +27,7 @@ def library():
 
 def declared_functions() -> list[str]:
     text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
-    return re.findall(r"^(?:int|const char\*)\s+(cfm_\w+)\s*\(", text, flags=re.M)
+    return re.findall(r"^(?:int|int64_t|const char\*)\s+(cfm_\w+)\s*\(", text, flags=re.M)
 
 
 def test_header_declares_the_entry_points_the_binding_uses():

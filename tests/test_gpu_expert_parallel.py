@@ -19,7 +19,7 @@ def _free_port() -> int:
         return int(sock.getsockname()[1])
 
 
-def _worker(rank, world, port, name, strategy, results):
+def _worker(rank, world, port, name, strategy, exchange, results):
     import faulthandler
     import os
     import sys
@@ -61,14 +61,18 @@ def _worker(rank, world, port, name, strategy, results):
             case.gate_up[span].to(device), channel_major(item["down"][span]),
             case.encoder[span].to(device) if case.encoder is not None else None,
             case.decoder.to(device) if case.decoder is not None else None,
-            case.plan, tokens, global_experts=experts, screen=strategy,
+            case.plan, tokens, global_experts=experts, screen=strategy, exchange=exchange,
             sketch=(item["codes"][span].to(device), statistics(item["statistics"][span])),
             activation=case.activation, selection_score="point",
         )
+        assert (sharded.exchange is not None) == (exchange == "peer")
         padding = case.padding[rows].to(device) if case.padding is not None else None
-        out = sharded(case.hidden[rows].to(device), case.ids[rows].to(device),
-                      case.weights[rows].to(device), padding)
-        torch.cuda.synchronize()
+        for _ in range(2 if exchange == "peer" else 1):  # two epochs of the exchange
+            out = sharded(case.hidden[rows].to(device), case.ids[rows].to(device),
+                          case.weights[rows].to(device), padding)
+            torch.cuda.synchronize()
+        if sharded.exchange is not None:
+            assert sharded.exchange.status() == 0  # no wait ran out
         total = world * tokens
         kept_local = (sharded.reader.ids[:total].cpu() >= 0)
         if strategy == "sharded":
@@ -127,15 +131,16 @@ def _worker(rank, world, port, name, strategy, results):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("strategy", ["replicated", "sharded"])
+@pytest.mark.parametrize("strategy,exchange", [("replicated", "collective"),
+                                               ("replicated", "peer"), ("sharded", "collective")])
 @pytest.mark.parametrize("name", ["qwen35-e16-t4", "qwen3-e16-t8", "graph-routes"])
-def test_sharded_reader_matches_single_gpu(name, strategy):
+def test_sharded_reader_matches_single_gpu(name, strategy, exchange):
     from helpers import prepared
 
     world = 2
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(_worker, args=(world, _free_port(), name, strategy, results), nprocs=world,
+    mp.spawn(_worker, args=(world, _free_port(), name, strategy, exchange, results), nprocs=world,
              join=True)
     case = prepared(name)["case"]
     reference, kept, scores, selected = results[0][6]

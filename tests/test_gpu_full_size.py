@@ -130,6 +130,18 @@ def test_full_size_layer_properties_and_oracle_sample(oracle):
     check_oracle_sample(oracle, reader, plan, (gate_up, down, encoder, decoder),
                         (hidden, ids, weights), out, sample)
 
+    # Four tokens per expert on average: the default walks the rows per token.  The
+    # expert-major kernels on the same batch keep the same channels and agree on the output.
+    grouped = ProgressiveReader(gate_up, down, encoder, decoder, plan, tokens,
+                                selection_score="point", sketch=sketch, row_engine="expert_major")
+    other = grouped(hidden, ids, weights).clone()
+    torch.cuda.synchronize()
+    assert torch.equal(grouped.candidate_ids[-1][:tokens], lists)
+    assert torch.equal(grouped.latent[:tokens], reader.latent[:tokens])
+    torch.testing.assert_close(other.float(), out.float(), rtol=PATH_RTOL, atol=PATH_ATOL)
+    check_oracle_sample(oracle, grouped, plan, (gate_up, down, encoder, decoder),
+                        (hidden, ids, weights), other, sample)
+
 
 def test_qwen35_shape_batch_256_and_smaller_batches(oracle):
     """256 experts of width 512, Student-t inputs, router bias: one call of 256 tokens, then
