@@ -570,6 +570,47 @@ def expert_parallel_parity(shape, plan, world: int, rank: int, device) -> dict:
             "experts": small.experts, "tokens_per_rank": tokens, "max_abs_difference_rank0": worst}
 
 
+def expert_parallel_timeline(sharded, batches, stream, repeats: int = 50) -> dict:
+    """Median microseconds between the stage boundaries of eager expert-parallel steps.
+
+    Every stage of `ExpertParallelReader` reports when it has been enqueued; a CUDA
+    event recorded there on the launching stream closes the interval that stage's
+    kernels (or collective) occupy on that stream.  Work on the side stream (the
+    recovery encoder) overlaps and has no interval of its own.
+    """
+    import torch.distributed as dist
+
+    names: list[str] = []
+    intervals: dict[str, list[float]] = {}
+    layers = len(sharded)
+    with torch.cuda.stream(stream):
+        for repeat in range(repeats + 5):
+            reader = sharded[repeat % layers]
+            events = [("start", torch.cuda.Event(enable_timing=True))]
+            dist.barrier()
+            torch.cuda.synchronize()
+            events[0][1].record(stream)
+
+            def trace(name, events=events):
+                event = torch.cuda.Event(enable_timing=True)
+                event.record(stream)
+                events.append((name, event))
+
+            reader.engine.trace = trace
+            reader(*batches[repeat % layers])
+            reader.engine.trace = None
+            stream.synchronize()
+            if repeat < 5:
+                continue
+            for (_, before), (name, after) in zip(events, events[1:]):
+                if name not in intervals:
+                    names.append(name)
+                intervals.setdefault(name, []).append(1e3 * before.elapsed_time(after))
+            intervals.setdefault("whole step", []).append(
+                1e3 * events[0][1].elapsed_time(events[-1][1]))
+    return {name: round(median(intervals[name]), 2) for name in names + ["whole step"]}
+
+
 def run_ours(args, shape, plans) -> None:
     import ctypes
 
@@ -634,7 +675,11 @@ def run_ours(args, shape, plans) -> None:
                 batches.append(packed_batch(device_batch(shape, router, tokens, g, device)))
             line = measure(args, shape, plan, tokens, readers, sharded, batches, stream,
                            rank, world, local)
+            timeline = (expert_parallel_timeline(sharded, batches, stream)
+                        if distributed and args.timeline else None)
             if rank == 0:
+                if timeline is not None:
+                    line["timeline_us"] = timeline
                 if parity is not None:
                     line["parity_checked"] = True
                     line["parity"] = parity
@@ -867,6 +912,8 @@ def main() -> None:
     parser.add_argument("--no-gpu-comparator", action="store_true")
     parser.add_argument("--tensor-engine", default="mma_sync", choices=("mma_sync", "tcgen05"),
                         help="tensor-core path of the expert-major screen")
+    parser.add_argument("--timeline", action="store_true",
+                        help="expert parallel: also time every stage of eager steps on rank 0")
     parser.add_argument("--exchange", default="auto", choices=("auto", "peer", "collective"),
                         help="expert parallel: kept lists and partial rows over peer memory "
                              "or by NCCL collectives")

@@ -16,7 +16,7 @@ from pathlib import Path
 PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE / "csrc" / "cfm_grouped.cuh",
-           PACKAGE / "csrc" / "cfm_exchange.cuh",
+           PACKAGE / "csrc" / "cfm_exchange.cuh", PACKAGE / "csrc" / "cfm_select.cuh",
            PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
 ABI_VERSION = 9
@@ -112,6 +112,7 @@ _LAYOUT_ARRAYS = (
     "counters", "partial", "scores", "selected", "completed", "candidate_ids", "counts",
     "starts", "tile_starts", "activations", "exact", "down_parts", "encoder_parts", "latent",
     "status", "limbs", "group_offsets", "group_pairs", "cuts", "variances", "unscales", "zero_limbs",
+    "tile_list", "tile_count",
 )
 
 

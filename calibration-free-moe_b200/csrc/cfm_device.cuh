@@ -142,4 +142,32 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) {
   return __uint_as_float(w & 0xffff0000u);
 }
 
+// Exclusive scan of `value` over the CTA (blockDim.x a multiple of 32, at most
+// 1024); `scratch` holds 33 ints.  Returns the sum of the earlier threads and
+// writes the CTA total to `*total`.  Ends with a barrier.
+__device__ __forceinline__ int block_exclusive_scan(int value, int* scratch, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  int scan = value;
+#pragma unroll
+  for (int w = 1; w < 32; w <<= 1) {
+    const int o = __shfl_up_sync(kFull, scan, w);
+    if (lane >= w) scan += o;
+  }
+  __syncthreads();  // earlier users of the scratch are done
+  if (lane == 31) scratch[warp] = scan;
+  __syncthreads();
+  if (warp == 0) {
+    int t = lane < warps ? scratch[lane] : 0;
+#pragma unroll
+    for (int w = 1; w < 32; w <<= 1) {
+      const int o = __shfl_up_sync(kFull, t, w);
+      if (lane >= w) t += o;
+    }
+    scratch[lane] = t;  // inclusive scan of the warp totals
+  }
+  __syncthreads();
+  *total = scratch[warps - 1];
+  return scan - value + (warp ? scratch[warp - 1] : 0);
+}
+
 }  // namespace cfm

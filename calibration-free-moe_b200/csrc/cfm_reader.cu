@@ -62,6 +62,8 @@ struct Workspace {
   float* variances;
   float* unscales;
   int8_t* zero_limbs;
+  int32_t* tile_list;
+  int32_t* tile_count;
   int32_t parts_tokens;
   int32_t down_tiles;
   int32_t encoder_tiles;
@@ -157,6 +159,8 @@ static int make_layout(const cfm_layer* l, int32_t capacity, cfm_workspace_layou
   o->variances = take(4 * C * 2 * N);
   o->unscales = take(4 * C * B);
   o->zero_limbs = take(B * 3 * kBlock);
+  o->tile_list = take(32 * C * ((F + kDownTileRows - 1) / kDownTileRows + K));
+  o->tile_count = take(16);
   o->bytes = at;
   return 0;
 }
@@ -194,6 +198,8 @@ static Workspace bind(const cfm_workspace_layout& o, void* base, int32_t capacit
   w.variances = reinterpret_cast<float*>(p + o.variances);
   w.unscales = reinterpret_cast<float*>(p + o.unscales);
   w.zero_limbs = reinterpret_cast<int8_t*>(p + o.zero_limbs);
+  w.tile_list = reinterpret_cast<int32_t*>(p + o.tile_list);
+  w.tile_count = reinterpret_cast<int32_t*>(p + o.tile_count);
   w.parts_tokens = o.parts_tokens;
   w.down_tiles = o.down_tiles;
   w.encoder_tiles = o.encoder_tiles;
@@ -637,8 +643,12 @@ __global__ void __launch_bounds__(512) k_screen(Layer L, Workspace ws, const uin
 // Lists the active (token, slot) pairs of every local expert.  One CTA; dynamic
 // shared memory: 2 * E counters.  The order of an expert's pairs is whatever the
 // atomics produce; every pair's result is independent of it.
+// With `with_tiles` (the kept counts are already known: the selection was adopted)
+// the CTA goes on to list the call's down tiles (cfm_select.cuh).
+__device__ __forceinline__ void list_down_tiles(const Layer& L, const Workspace& ws, int* scratch);
+
 __global__ void __launch_bounds__(1024) k_group(Layer L, Workspace ws, const uint8_t* padding,
-                                                int T) {
+                                                int T, int with_tiles) {
   extern __shared__ int group_smem[];
   int* count = group_smem;
   int* cursor = group_smem + L.E;
@@ -672,7 +682,14 @@ __global__ void __launch_bounds__(1024) k_group(Layer L, Workspace ws, const uin
   __syncthreads();
   for (int p = tid; p < pairs; p += blockDim.x) {
     const int e = ws.ids[p];
-    if (e >= 0 && !(padding && padding[p / L.K])) ws.group_pairs[atomicAdd(&cursor[e], 1)] = p;
+    if (e >= 0 && !(padding && padding[p / L.K])) {
+      ws.group_pairs[atomicAdd(&cursor[e], 1)] = p;
+    }
+  }
+  if (with_tiles) {
+    __threadfence_block();
+    __syncthreads();  // group_offsets and group_pairs are read back below
+    list_down_tiles(L, ws, group_smem);
   }
 }
 
@@ -1197,7 +1214,60 @@ __device__ __forceinline__ float candidate_score(const Layer& L, const Workspace
 // ---------------------------------------------------------------------------
 constexpr int kSelectThreads = 1024;
 
+#include "cfm_select.cuh"
+
 __device__ __forceinline__ int64_t sector_run(int64_t bytes) { return (bytes + 31) / 32 * 32; }
+
+// Read-cost counters of one token (integers, so FP64 atomics are exact): lane
+// `lane` of one warp adds slot `lane` of `read_work`.  `local_slots` of the
+// token's experts are held here and `kept_local` of its kept channels are theirs.
+__device__ __forceinline__ void account_reads(const Layer& L, int lane, int local_slots,
+                                              int kept_local, bool screened) {
+  const int I = L.I, K = L.K;
+  if (L.read_work && lane < CFM_READ_WORK_SLOTS) {
+    const bool ep = L.expert_map != nullptr;
+    const int64_t H = L.H, R = L.R;
+    const int64_t candidates = static_cast<int64_t>(local_slots) * I;
+    const int64_t native = 2 * (2 * kept_local * H + kept_local * H);
+    const int64_t dense_slot = 6 * static_cast<int64_t>(I) * H;
+    const int64_t reference = ep ? local_slots * dense_slot : K * dense_slot;
+    const int64_t recovery = 2 * R * (candidates - kept_local + (L.owner ? H : 0));
+    const bool residual = L.score != CFM_SCORE_POINT;
+    const int64_t code = 2 * ((I + 4) / 5), plane = 4 * I;
+    const int64_t sketch_exact =
+        screened ? local_slots * L.B * (L.KEEP * code + plane * (1 + residual)) : 0;
+    const int64_t sketch_sector =
+        screened ? local_slots * L.B *
+                       (L.KEEP * sector_run(code) + sector_run(plane) * (1 + residual))
+                 : 0;
+    // Bytes the screen kernel itself requests: 2-bit codes (I / 2 bytes per
+    // kept coordinate) and the FP16 scale plane.
+    const int64_t sketch_issued =
+        screened ? local_slots * L.B * (static_cast<int64_t>(L.KEEP) * (I / 2) + plane) : 0;
+    const int64_t selection =
+        screened ? ((L.geometry ? 12 : 4) * candidates) : 0;
+    // Threshold mode: every token also reads the FP32 layer threshold (one sector).
+    const int64_t threshold_exact = L.threshold ? 4 : 0, threshold_sector = L.threshold ? 32 : 0;
+    int64_t value = 0;
+    switch (lane) {
+      case 0: case 6: value = native; break;
+      case 1: value = reference; break;
+      case 3: case 7: value = recovery; break;
+      case 4: value = selection + threshold_exact; break;
+      case 9: value = selection + threshold_sector; break;
+      case 19: value = L.threshold ? 1 : 0; break;
+      case 5: value = sketch_exact; break;
+      case 10: value = screened ? H : 0; break;
+      case 11: value = sketch_issued; break;
+      case 17: value = sketch_sector; break;
+      case 12: value = 4 * H * kept_local; break;
+      case 13: value = 2 * H * kept_local; break;
+      case 14: value = 2 * R * (candidates - kept_local); break;
+      default: value = 0;
+  }
+    if (value) atomicAdd(L.read_work + lane, static_cast<double>(value));
+  }
+}
 
 // grid (T), 1024 threads, dynamic shared memory: N keys.
 __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws,
@@ -1425,49 +1495,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
       local_slots += __shfl_xor_sync(kFull, local_slots, w);
       kept_local += __shfl_xor_sync(kFull, kept_local, w);
     }
-    if (L.read_work && lane < CFM_READ_WORK_SLOTS) {
-      const bool ep = L.expert_map != nullptr;
-      const int64_t H = L.H, R = L.R;
-      const int64_t candidates = static_cast<int64_t>(local_slots) * I;
-      const int64_t native = 2 * (2 * kept_local * H + kept_local * H);
-      const int64_t dense_slot = 6 * static_cast<int64_t>(I) * H;
-      const int64_t reference = ep ? local_slots * dense_slot : K * dense_slot;
-      const int64_t recovery = 2 * R * (candidates - kept_local + (L.owner ? H : 0));
-      const bool residual = L.score != CFM_SCORE_POINT;
-      const int64_t code = 2 * ((I + 4) / 5), plane = 4 * I;
-      const int64_t sketch_exact =
-          screened ? local_slots * L.B * (L.KEEP * code + plane * (1 + residual)) : 0;
-      const int64_t sketch_sector =
-          screened ? local_slots * L.B *
-                         (L.KEEP * sector_run(code) + sector_run(plane) * (1 + residual))
-                   : 0;
-      // Bytes the screen kernel itself requests: 2-bit codes (I / 2 bytes per
-      // kept coordinate) and the FP16 scale plane.
-      const int64_t sketch_issued =
-          screened ? local_slots * L.B * (static_cast<int64_t>(L.KEEP) * (I / 2) + plane) : 0;
-      const int64_t selection =
-          screened ? ((L.geometry ? 12 : 4) * candidates) : 0;
-      // Threshold mode: every token also reads the FP32 layer threshold (one sector).
-      const int64_t threshold_exact = L.threshold ? 4 : 0, threshold_sector = L.threshold ? 32 : 0;
-      int64_t value = 0;
-      switch (lane) {
-        case 0: case 6: value = native; break;
-        case 1: value = reference; break;
-        case 3: case 7: value = recovery; break;
-        case 4: value = selection + threshold_exact; break;
-        case 9: value = selection + threshold_sector; break;
-        case 19: value = L.threshold ? 1 : 0; break;
-        case 5: value = sketch_exact; break;
-        case 10: value = screened ? H : 0; break;
-        case 11: value = sketch_issued; break;
-        case 17: value = sketch_sector; break;
-        case 12: value = 4 * H * kept_local; break;
-        case 13: value = 2 * H * kept_local; break;
-        case 14: value = 2 * R * (candidates - kept_local); break;
-        default: value = 0;
-      }
-      if (value) atomicAdd(L.read_work + lane, static_cast<double>(value));
-    }
+    account_reads(L, lane, local_slots, kept_local, screened);
   }
 }
 
@@ -1634,20 +1662,16 @@ constexpr int kDownColumns = 1024;  // output columns per CTA: 32 accumulators p
 // order through shared memory.  Under expert parallelism
 // (STRIDED) fewer CTAs than tiles are launched per token, since a rank owns few
 // of a token's slots; they walk the tiles in strides.
-// One tile: up to 64 kept rows of slot `slot` of token t, starting at position
-// `first` of the slot's part of the kept list, summed into down tile `tile`.
+// One tile: `rows` (at most 64) kept rows of slot `slot` of token t, an expert-e
+// slot, whose candidate ids start at `list`, summed into down tile `tile`.
 // Called by all 128 threads of a CTA; begins and ends with the shared arrays free.
 __device__ __forceinline__ void down_tile(const Layer& L, const Workspace& ws, int t, int slot,
-                                          int first, int tile, int* tile_channel,
-                                          float* tile_activation, float (*red)[kDownColumns]) {
+                                          int e, int rows, const int32_t* list, int tile,
+                                          int* tile_channel, float* tile_activation,
+                                          float (*red)[kDownColumns]) {
   constexpr int CHUNKS = kDownColumns / 256;  // 16-byte pieces per lane and row
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const size_t token_pairs = static_cast<size_t>(t) * L.K;
   const int column0 = blockIdx.x * kDownColumns + lane * 8;  // this lane's first column
-  const int e = ws.ids[token_pairs + slot];
-  const int rows = min(kDownTileRows, ws.counts[token_pairs + slot] - first);
-  const int32_t* list =
-      ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first;
   const __nv_bfloat16* act = ws.activations + static_cast<size_t>(t) * L.N;
   if (tid < rows) {
     const int cid = list[tid];
@@ -1754,27 +1778,26 @@ __global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const ui
     __syncthreads();
     const int slot = s_slot, first = s_first;
     if (slot < 0) continue;  // uniform: every thread read the same slot
-    down_tile(L, ws, t, slot, first, tile, tile_channel, tile_activation, red);
+    down_tile(L, ws, t, slot, ws.ids[token_pairs + slot],
+              min(kDownTileRows, ws.counts[token_pairs + slot] - first),
+              ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first,
+              tile, tile_channel, tile_activation, red);
   } while (STRIDED && (tile += gridDim.y) < used);
 }
 
-// The same tiles with the (token, expert) pairs walked in expert order:
-// grid (ceil(H / 1024), Y, T * K), 128 threads.  CTA layer z takes the z-th pair
-// of the list grouped by expert (k_group); its Y CTAs share the pair's tiles.
-// Tokens of one expert run next to each other in time, so a down row several of
-// them kept comes from HBM once and from L2 after that.  Same tiles, same sums,
-// same bits as k_down.
-__global__ void __launch_bounds__(128, 4) k_down_pairs(Layer L, Workspace ws) {
+// The same tiles from the list of the call's tiles in expert order
+// (cfm_select.cuh): grid (ceil(H / 1024), most tiles a call can have), 128
+// threads.  A CTA reads its 32-byte record and goes straight to the tile's rows.
+// Same tiles, same sums, same bits as k_down.
+__global__ void __launch_bounds__(128, 4) k_down_tiles(Layer L, Workspace ws) {
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
   __shared__ __align__(16) float red[4][kDownColumns];
-  if (static_cast<int>(blockIdx.z) >= ws.group_offsets[L.E]) return;
-  const int pair = ws.group_pairs[blockIdx.z];
-  const int tiles = (ws.counts[pair] + kDownTileRows - 1) / kDownTileRows;
-  const int t = pair / L.K, slot = pair - t * L.K;
-  const int begin = ws.tile_starts[pair];
-  for (int j = blockIdx.y; j < tiles; j += gridDim.y)
-    down_tile(L, ws, t, slot, j * kDownTileRows, begin + j, tile_channel, tile_activation, red);
+  if (static_cast<int>(blockIdx.y) >= ws.tile_count[0]) return;
+  const int4* record = reinterpret_cast<const int4*>(ws.tile_list) + 2 * blockIdx.y;
+  const int4 a = record[0], b = record[1];  // t, slot, expert, rows | list, tile
+  down_tile(L, ws, a.x, a.y, a.z, a.w, ws.candidate_ids + b.x, b.y, tile_channel,
+            tile_activation, red);
 }
 
 // ---------------------------------------------------------------------------
@@ -2178,7 +2201,7 @@ static int run_route(const Bound& b, const cfm_call* call) {
   int rc = launched();
   if (rc || !screens_grouped(b)) return rc;
   // The expert-major screen reads the (token, slot) pairs grouped by expert.
-  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
+  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T, 0);
   return launched();
 }
 
@@ -2255,6 +2278,8 @@ static int run_screen_projections(const Bound& b) {
   }
 }
 
+static bool pairs_grouped(const Bound& b);
+
 static int run_select(const Bound& b, int scores_ready) {
   const size_t smem = sizeof(uint32_t) * b.L.N;
   if (smem + 10240 > 48 * 1024) {  // static shared memory counts against the default limit
@@ -2267,6 +2292,13 @@ static int run_select(const Bound& b, int scores_ready) {
   return launched();
 }
 
+// The down tiles of the call in expert order, once the selection is done.
+static int run_list_tiles(const Bound& b) {
+  if (!pairs_grouped(b) || !b.L.down) return 0;  // a layer without native rows has no down stage
+  k_list_tiles<<<1, 1024, 0, b.stream>>>(b.L, b.ws);
+  return launched();
+}
+
 static int run_score(const Bound& b) {
   if (b.L.F >= b.L.N) return 0;
   k_score<<<dim3(b.T, (b.L.N + 255) / 256), 256, 0, b.stream>>>(b.L, b.ws, b.padding);
@@ -2275,16 +2307,16 @@ static int run_score(const Bound& b) {
 
 // Batches whose pairs are grouped by expert also read the experts' native rows
 // expert-major (the groups come from k_group, launched by route and adopt).
-static bool pairs_grouped(const Bound& b) { return screens_grouped(b); }
+static bool pairs_grouped(const Bound& b) { return screens_grouped(b); }  // see run_select
 
 // Expert-major exact, down and encode: a row is read once for all the tokens of
-// its expert that kept it.  Pays from about eight tokens per expert, where the
-// union of their kept channels is well below their sum; below that the per-token
-// kernels run, walking the pairs in expert order.
+// its expert that kept it.  On the shapes measured so far (4 to 16 tokens per
+// expert) the per-token kernels walking the pairs in expert order are faster: the
+// rows several tokens share come from HBM once either way (from L2 after the
+// first), and the per-token kernels keep more loads in flight.  So the automatic
+// choice is per-token; the expert-major kernels run on request.
 static bool rows_grouped(const Bound& b) {
-  if (!pairs_grouped(b) || b.L.row_engine == CFM_ROWS_PER_TOKEN) return false;
-  if (b.L.row_engine == CFM_ROWS_EXPERT_MAJOR) return true;
-  return static_cast<int64_t>(b.T) * b.L.K >= 8 * static_cast<int64_t>(b.L.E);
+  return pairs_grouped(b) && b.L.row_engine == CFM_ROWS_EXPERT_MAJOR;
 }
 
 // Partial sums per (token, local slot) of the expert-major down kernel: enough
@@ -2363,11 +2395,10 @@ static int run_down(const Bound& b) {
     return launched();
   }
   if (pairs_grouped(b)) {
-    // Tiles per pair at the mean number of kept rows, one more for the busy slots.
-    const int per_pair = (b.L.F + b.L.K - 1) / b.L.K;
-    const int share = (per_pair + kDownTileRows - 1) / kDownTileRows + 1;
-    const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, share, b.T * b.L.K);
-    k_down_pairs<<<grid, 128, 0, b.stream>>>(b.L, b.ws);
+    // The call's tiles were listed in expert order after the selection.
+    const int most = b.T * ((b.L.F + kDownTileRows - 1) / kDownTileRows + b.L.K);
+    const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, most);
+    k_down_tiles<<<grid, 128, 0, b.stream>>>(b.L, b.ws);
     return launched();
   }
   int tiles = b.ws.down_tiles;
@@ -2417,7 +2448,7 @@ static int run_output(const Bound& b, const cfm_call* call) {
 // call on that device (make that call outside stream capture).
 struct SideStream {
   cudaStream_t stream;
-  cudaEvent_t fork, join;
+  cudaEvent_t fork, join, tiles;
   std::mutex* sequence;  // held while a whole-layer call enqueues its fork .. join sequence
   bool ready;
 };
@@ -2438,7 +2469,8 @@ static int side_stream(SideStream* out) {
       return -1;
     }
     if (cudaEventCreateWithFlags(&slot.fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&slot.join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaEventCreateWithFlags(&slot.join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&slot.tiles, cudaEventDisableTiming) != cudaSuccess) {
       (void)cudaGetLastError();
       return -1;
     }
@@ -2507,7 +2539,11 @@ int cfm_workspace_layout_for(const cfm_layer* layer, int32_t capacity,
 CFM_STAGE(cfm_prepare_input, return run_prepare(b, call);)
 CFM_STAGE(cfm_route, return run_route(b, call);)
 CFM_STAGE(cfm_screen, return run_screen(b);)
-CFM_STAGE(cfm_select, return run_select(b, call->scores_ready);)
+CFM_STAGE(cfm_select, {
+  const int code = run_select(b, call->scores_ready);
+  // Mode 3 only publishes the cut; every other mode leaves final counts behind.
+  return code || call->scores_ready == 3 ? code : run_list_tiles(b);
+})
 CFM_STAGE(cfm_score, return run_score(b);)
 CFM_STAGE(cfm_exact, return run_exact(b, call);)
 CFM_STAGE(cfm_down, return run_down(b);)
@@ -2563,7 +2599,7 @@ int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const c
   int code = launched();
   if (code || !pairs_grouped(b)) return code;
   // The exact and down kernels read the pairs grouped by expert.
-  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
+  k_group<<<1, 1024, sizeof(int) * std::max(2 * b.L.E, 40), b.stream>>>(b.L, b.ws, b.padding, b.T, 1);
   return launched();
 }
 
@@ -2694,14 +2730,21 @@ int cfm_reader_forward(const cfm_layer* layer, void* workspace, int32_t capacity
   }
   if ((rc = run_screen(b))) return rc;
   if ((rc = run_select(b, 0))) return rc;
-  // The recovery encoder (L2-resident rows, arithmetic) runs beside the two
-  // HBM-bound gathers on the side stream and joins before the output mix.
-  const bool fork = b.L.R > 0 && have_side;
+  // The listing of the down tiles and the recovery encoder (L2-resident rows,
+  // arithmetic) run on the side stream beside the two HBM-bound gathers; the down
+  // kernel waits for the list, the output mix for the encoder.
+  const bool fork = have_side && (b.L.R > 0 || pairs_grouped(b));
   if (fork) {
     if ((rc = fork_side())) return leave(rc);
+    if ((rc = run_list_tiles(on_side))) return leave(rc);
+    if (cudaEventRecord(side.tiles, side.stream) != cudaSuccess) return leave(static_cast<int>(cudaGetLastError()));
     if ((rc = run_encode(on_side))) return leave(rc);
+  } else if ((rc = run_list_tiles(b))) {
+    return rc;
   }
   if ((rc = run_exact(b, call))) return leave(rc);
+  if (fork && cudaStreamWaitEvent(b.stream, side.tiles, 0) != cudaSuccess)
+    return leave(static_cast<int>(cudaGetLastError()));
   if ((rc = run_down(b))) return leave(rc);
   if (fork) {
     if ((rc = join_side())) return leave(rc);

@@ -189,6 +189,9 @@ def replicated_screen_forward(
         pending.append(_start_gather_rows(lists, world, group))
     for _, work in pending:
         work.wait()
+    mark = getattr(engine, "_mark", None)
+    if mark is not None:
+        mark("all_gather of rows, routes" + ("" if peers else " and lists") + " complete")
     all_hidden, all_ids, all_weights = (gathered for gathered, _ in pending[:3])
     all_padding = pending[3][0].view(torch.bool) if padding is not None else None
     all_lists = None if peers else pending[-1][0]
@@ -196,6 +199,8 @@ def replicated_screen_forward(
     if peers:  # the rows are already in the home ranks' blocks
         return engine.finish(None)
     mine = _reduce_scatter_in_place(routed, world, rank, group)
+    if mark is not None:
+        mark("reduce_scatter")
     return engine.finish(mine)
 
 
@@ -420,6 +425,12 @@ class ReplicatedScreenEngine:
         self._side = torch.cuda.Stream(device, priority=-1)
         self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
         self._library = owner._library
+        # Called with a stage name after each stage is enqueued (timelines); None = off.
+        self.trace = None
+
+    def _mark(self, name: str) -> None:
+        if self.trace is not None:
+            self.trace(name)
 
     def _home_stage(self, name: str, call: _native.Call) -> None:
         home, device = self.home, self.owner._device
@@ -443,15 +454,19 @@ class ReplicatedScreenEngine:
             if screened:
                 self._home_stage("cfm_prepare_input", call)
             self._home_stage("cfm_route", call)
+            self._mark("prepare + route")
             if screened:
                 self._home_stage("cfm_screen", call)
+            self._mark("screen")
             self._home_stage("cfm_select", call)
+            self._mark("select")
             if self.exchange is not None:
                 if rows != self.exchange.tokens:
                     raise ValueError("The peer-memory exchange needs the full batch on every rank "
                                      "(use `padding` for ragged batches)")
                 call.exchange = ctypes.addressof(self.exchange.struct)
                 self._home_stage("cfm_exchange_send_lists", call)
+                self._mark("send lists (peer stores)")
             if home.rank:
                 main = torch.cuda.current_stream(device)
                 self._fork.record(main)
@@ -474,6 +489,8 @@ class ReplicatedScreenEngine:
         with torch.cuda.device(owner._device):
             for stage in ("cfm_adopt", "cfm_exact", "cfm_down", "cfm_partial_output"):
                 owner._stage(stage, call)
+                self._mark(stage[4:] + (" (waits for the lists)" if stage == "cfm_adopt"
+                                        and self.exchange is not None else ""))
         return self._routed[:rows]
 
     def finish(self, routed):
@@ -491,6 +508,7 @@ class ReplicatedScreenEngine:
                     ctypes.c_void_p(main.cuda_stream),
                 )
                 _native.check(code, "cfm_finish_rows")
+                self._mark("finish (waits for the rows)")
                 return out
             code = self._library.cfm_finish(
                 ctypes.byref(home.layer), rows, routed.data_ptr(),
@@ -498,6 +516,7 @@ class ReplicatedScreenEngine:
                 ctypes.c_void_p(main.cuda_stream),
             )
         _native.check(code, "cfm_finish")
+        self._mark("finish")
         return out
 
 

@@ -84,6 +84,7 @@ _TORCH_TYPES = {
     "latent": torch.float32, "status": torch.int32, "limbs": torch.int8,
     "group_offsets": torch.int32, "group_pairs": torch.int32, "cuts": torch.int32,
     "variances": torch.float32, "unscales": torch.float32, "zero_limbs": torch.int8,
+    "tile_list": torch.int32, "tile_count": torch.int32,
 }
 
 
@@ -152,6 +153,7 @@ class ReaderWorkspace:
             "status": (4,), "limbs": (c, blocks, 3, 128),
             "group_offsets": (self.experts + 1,), "group_pairs": (c * k,), "cuts": (c, k + 1),
             "variances": (c, 2, n), "unscales": (c, blocks), "zero_limbs": (blocks, 3, 128),
+            "tile_list": (c * (-(-f // 64) + k), 8), "tile_count": (4,),
         }
         for name, shape in shapes.items():
             setattr(target, name, self._view(layout, name, shape))
@@ -250,7 +252,7 @@ class ProgressiveReader:
         rows: "expert_major" (a row several tokens of one expert kept is read once
         for all of them), "per_token" (one gather per token, tokens of one expert
         next to each other in time so that shared rows meet in L2) or "auto"
-        (expert-major from eight tokens per expert on average).  The kept channels
+        (the faster one on the shapes measured so far: per token).  The kept channels
         do not depend on it; outputs differ by FP32 summation order only.
 
         Contract violations raise ValueError before anything is launched.

@@ -43,7 +43,7 @@ extern "C" {
 #define CFM_SCORE_RECOVERY_AWARE 1
 #define CFM_ENGINE_MMA_SYNC 0 /* warp-level mma.sync.m16n8k32 (default: measured faster) */
 #define CFM_ENGINE_TCGEN05 1  /* tcgen05.mma kind::i8, accumulators in tensor memory     */
-#define CFM_ROWS_AUTO 0        /* expert-major from eight tokens per expert on average */
+#define CFM_ROWS_AUTO 0        /* the library's choice (per token, pairs in expert order) */
 #define CFM_ROWS_PER_TOKEN 1   /* native rows always gathered per token                 */
 #define CFM_ROWS_EXPERT_MAJOR 2 /* expert-major whenever the pairs are grouped (T >= 8) */
 #define CFM_READ_WORK_SLOTS 20
@@ -159,8 +159,10 @@ typedef struct cfm_workspace_layout {
   int64_t variances;      /* f32 [C, 2, N] residual variances of the projections */
   int64_t unscales;       /* f32 [C, B] 2^(exponent - 21), undoes the fixed point */
   int64_t zero_limbs;     /* i8  [B, 3, 128] zero digits for empty token slots    */
+  int64_t tile_list;      /* i32 [C * (ceil(F / 64) + K), 8] down tiles in expert order */
+  int64_t tile_count;     /* i32 [4] number of listed tiles                        */
   int32_t parts_tokens;   /* tokens the split screen can serve                  */
-  int32_t down_tiles;     /* ceil(F / 128) + K - 1                              */
+  int32_t down_tiles;     /* max(ceil(F / 64) + K - 1, 8 K) partial sums per token */
   int32_t encoder_tiles;  /* ceil(I / 256)                                      */
   int32_t reserved;
 } cfm_workspace_layout;
