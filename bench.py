@@ -438,6 +438,7 @@ def run_triton(args, shape, plan) -> None:
             for index in range(layers):
                 readers.append(TritonReader(*weights_of_layer[index], reference_plan, tokens,
                                             **options))
+            torch.cuda.synchronize()  # built on the default stream, used on `stream`
             for index in range(layers):
                 step(index)
             stream.synchronize()
@@ -628,6 +629,9 @@ def run_ours(args, shape, plans) -> None:
     if distributed:
         import torch.distributed as dist
 
+        # The small all_gathers left on NCCL gain nothing from in-switch reduction, and
+        # ranks of this benchmark leave without tearing the communicator down.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=device)
         parity = expert_parallel_parity(shape, plans[0][1], world, rank, device)
         if not (parity["lists_equal"] and parity["outputs_close"]):
@@ -673,6 +677,10 @@ def run_ours(args, shape, plans) -> None:
             for index in range(layers):
                 router, g = weights_of_layer[index][4:6]
                 batches.append(packed_batch(device_batch(shape, router, tokens, g, device)))
+            # Readers and batches were made on the default stream and are used on the
+            # benchmark's own (non-blocking) stream from here on: their construction,
+            # the zero fill of the workspaces included, has to be complete first.
+            torch.cuda.synchronize()
             line = measure(args, shape, plan, tokens, readers, sharded, batches, stream,
                            rank, world, local)
             timeline = (expert_parallel_timeline(sharded, batches, stream)
@@ -908,6 +916,8 @@ def main() -> None:
     parser.add_argument("--screen-keep", type=float, default=None)
     parser.add_argument("--budgets", default=None,
                         help="comma-separated retention:screen_keep pairs: one line each")
+    parser.add_argument("--quick", action="store_true",
+                        help="three samples of 0.1 s instead of seven of 0.3 s (for long sweeps)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-gpu-comparator", action="store_true")
     parser.add_argument("--tensor-engine", default="mma_sync", choices=("mma_sync", "tcgen05"),
@@ -920,6 +930,9 @@ def main() -> None:
     parser.add_argument("--row-engine", default="auto", choices=("auto", "per_token", "expert_major"),
                         help="how batches of eight tokens and more read the native rows")
     args = parser.parse_args()
+    if args.quick:
+        global SAMPLES, SAMPLE_SECONDS
+        SAMPLES, SAMPLE_SECONDS = 3, 0.1
     shape = synthetic.CONFIGS[args.config]
 
     def plan_for(retention, screen_keep):

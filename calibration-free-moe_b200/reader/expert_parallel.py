@@ -461,9 +461,11 @@ class ReplicatedScreenEngine:
             self._home_stage("cfm_select", call)
             self._mark("select")
             if self.exchange is not None:
-                if rows != self.exchange.tokens:
-                    raise ValueError("The peer-memory exchange needs the full batch on every rank "
-                                     "(use `padding` for ragged batches)")
+                # Every rank brings the same number of rows to a call (as the collectives
+                # require too); the blocks are laid out for that number, up to their capacity.
+                if rows > self.exchange.tokens:
+                    raise ValueError("Sparse input exceeds the prepared token/candidate contract")
+                self.exchange.struct.tokens = rows
                 call.exchange = ctypes.addressof(self.exchange.struct)
                 self._home_stage("cfm_exchange_send_lists", call)
                 self._mark("send lists (peer stores)")
@@ -534,7 +536,7 @@ class ExpertParallelReader:
     exchange scores).  Both keep the same channels.  `exchange` picks how the
     replicated screen moves the kept lists and the partial rows: "peer" (kernels
     of the library over memory the ranks map from each other; every call must
-    then bring exactly `max_tokens` rows), "collective" (`all_gather` and
+    then bring the same number of rows on all ranks), "collective" (`all_gather` and
     `reduce_scatter`) or "auto" (peer memory when the group runs over NCCL and
     the mapping works).
     """
