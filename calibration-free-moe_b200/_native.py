@@ -17,6 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE / "csrc" / "cfm_grouped.cuh",
            PACKAGE / "csrc" / "cfm_exchange.cuh", PACKAGE / "csrc" / "cfm_select.cuh",
+           PACKAGE / "csrc" / "cfm_build.cuh",
            PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
 ABI_VERSION = 9
@@ -33,7 +34,7 @@ STAGES = (
     "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_adopt", "cfm_reader_forward",
     "cfm_exchange_send_lists",
 )
-PEER_SYMBOLS = ("cfm_exchange_bytes", "cfm_peer_alloc", "cfm_peer_export", "cfm_peer_import",
+PEER_SYMBOLS = ("cfm_build_sketch", "cfm_exchange_bytes", "cfm_peer_alloc", "cfm_peer_export", "cfm_peer_import",
                 "cfm_peer_release", "cfm_exchange_status", "cfm_finish_rows")
 SYMBOLS = (("cfm_abi_version", "cfm_error_string", "cfm_workspace_layout_for", "cfm_finish")
            + STAGES + PEER_SYMBOLS)
@@ -193,6 +194,11 @@ def load() -> ctypes.CDLL:
     library.cfm_finish.argtypes = [
         ctypes.POINTER(Layer), ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
         ctypes.c_void_p,
+    ]
+    library.cfm_build_sketch.restype = ctypes.c_int
+    library.cfm_build_sketch.argtypes = [
+        ctypes.POINTER(Layer), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+        ctypes.c_void_p, ctypes.c_void_p,
     ]
     library.cfm_exchange_bytes.restype = ctypes.c_int64
     library.cfm_exchange_bytes.argtypes = [ctypes.POINTER(Layer), ctypes.c_int32, ctypes.c_int32]

@@ -715,6 +715,8 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+#include "cfm_build.cuh"
+
 constexpr int kGroupWarps = 8;                   // 16 sketch rows per warp
 constexpr int kGroupRows = kGroupWarps * 16;     // rows per CTA
 constexpr int kGroupThreads = kGroupWarps * 32;
@@ -2600,6 +2602,20 @@ int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const c
   if (code || !pairs_grouped(b)) return code;
   // The exact and down kernels read the pairs grouped by expert.
   k_group<<<1, 1024, sizeof(int) * std::max(2 * b.L.E, 40), b.stream>>>(b.L, b.ws, b.padding, b.T, 1);
+  return launched();
+}
+
+int cfm_build_sketch(const cfm_layer* layer, const void* gate_up, const int8_t* signs,
+                     uint32_t* sketch, uint32_t* sketch_grouped, void* statistics, void* stream) {
+  if (!layer || !gate_up || !signs || !sketch || !sketch_grouped || !statistics) return CFM_E_NULL;
+  const int64_t H = layer->hidden, I = layer->width, E = layer->experts;
+  if (H <= 0 || H % kBlock || I <= 0 || I % 16 || E < 1 || E > 65535 || 2 * I / kBuildRows > 65535)
+    return CFM_E_SHAPE;
+  const dim3 grid(static_cast<unsigned>(H / kBlock), static_cast<unsigned>(2 * I / kBuildRows),
+                  static_cast<unsigned>(E));
+  k_build_sketch<<<grid, kBuildRows * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<int>(H), static_cast<int>(I), static_cast<const __nv_bfloat16*>(gate_up), signs,
+      sketch, sketch_grouped, static_cast<__half*>(statistics));
   return launched();
 }
 

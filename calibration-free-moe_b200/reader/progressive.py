@@ -23,7 +23,10 @@ from torch import Tensor
 from .. import _native
 from ..activation import ACTIVATION_CODES, GatedActivation
 from .budget import BudgetPlan
-from .sketch import block_hadamard_signs, build_sketch, repack_sketch, repack_sketch_grouped
+from .sketch import (
+    block_hadamard_signs, build_sketch, build_sketch_on_device, codes_from_words, repack_sketch,
+    repack_sketch_grouped,
+)
 from .budget import sketch_storage_bytes
 
 SelectionScore = Literal["recovery-aware", "point"]
@@ -228,6 +231,7 @@ class ProgressiveReader:
         retain_reference_sketch: bool = True,
         tensor_engine: str = "mma_sync",
         row_engine: str = "auto",
+        sketch_builder: str = "torch",
     ) -> None:
         """Prepare the sketch, norms and workspace of one layer.
 
@@ -254,6 +258,11 @@ class ProgressiveReader:
         next to each other in time so that shared rows meet in L2) or "auto"
         (the faster one on the shapes measured so far: per token).  The kept channels
         do not depend on it; outputs differ by FP32 summation order only.
+        `sketch_builder` picks who builds the sketch when none is given: "torch"
+        (tensor operations, byte-identical to the reference builder on the same
+        device) or "cuda" (the library's kernel, straight into the kernel layouts,
+        milliseconds per layer; single coordinates within rounding of the ternary
+        threshold may differ from the reference builder's).
 
         Contract violations raise ValueError before anything is launched.
         """
@@ -275,6 +284,8 @@ class ProgressiveReader:
             raise ValueError("tensor_engine must be 'mma_sync' or 'tcgen05'")
         if row_engine not in ROW_ENGINES:
             raise ValueError("row_engine must be 'auto', 'per_token' or 'expert_major'")
+        if sketch_builder not in ("torch", "cuda"):
+            raise ValueError("sketch_builder must be 'torch' or 'cuda'")
         if activation not in ACTIVATION_CODES:
             raise ValueError(f"Unsupported routed expert activation: {activation}")
         if screen_block_splits not in (1, 2, 4, 8) or grouped_screen_splits not in (1, 2, 4, 8):
@@ -334,29 +345,38 @@ class ProgressiveReader:
             self.recovery_owner = True
 
         self.sketch_signs = block_hadamard_signs(h, device)
-        if sketch is None:
-            sketch = build_sketch(gate_up, self.sketch_signs)
-        codes, statistics = sketch
         blocks = h // 128
-        if (
-            codes.shape != (e, sketch_storage_bytes(2 * i, h))
-            or codes.dtype != torch.uint8
-            or codes.device != device
-            or not codes.is_contiguous()
-            or statistics.shape != (e, 2 * i, blocks, 2)
-            or statistics.dtype != torch.float16
-            or statistics.device != device
-            or statistics.stride() != (4 * i * blocks, 1, 4 * i, 2 * i)
-        ):
-            raise ValueError("Sketch must match the local native routed experts")
+        if sketch is None and sketch_builder == "cuda":
+            # One pass of the library's kernel over the weights, straight into the kernel layouts.
+            self.sketch_words, grouped, statistics = build_sketch_on_device(gate_up, self.sketch_signs)
+            self.sketch_grouped_words = grouped if max_tokens >= GROUPED_SCREEN_MIN_TOKENS else None
+            self.sketch_codes = (
+                codes_from_words(self.sketch_words, 2 * i, h) if retain_reference_sketch else None
+            )
+        else:
+            if sketch is None:
+                sketch = build_sketch(gate_up, self.sketch_signs)
+            codes, statistics = sketch
+            if (
+                codes.shape != (e, sketch_storage_bytes(2 * i, h))
+                or codes.dtype != torch.uint8
+                or codes.device != device
+                or not codes.is_contiguous()
+                or statistics.shape != (e, 2 * i, blocks, 2)
+                or statistics.dtype != torch.float16
+                or statistics.device != device
+                or statistics.stride() != (4 * i * blocks, 1, 4 * i, 2 * i)
+            ):
+                raise ValueError("Sketch must match the local native routed experts")
+            # Kernel layout: two bits per trit, [E, H, 2I/16] words.
+            self.sketch_words = repack_sketch(codes, 2 * i, h)
+            # Row-major copy for the expert-major screen of batches of 8 tokens and more.
+            self.sketch_grouped_words = (
+                repack_sketch_grouped(codes, 2 * i, h)
+                if max_tokens >= GROUPED_SCREEN_MIN_TOKENS else None
+            )
+            self.sketch_codes = codes if retain_reference_sketch else None
         self.sketch_statistics = statistics
-        # Kernel layout: two bits per trit, [E, H, 2I/16] words.
-        self.sketch_words = repack_sketch(codes, 2 * i, h)
-        # Row-major copy for the expert-major screen of batches of 8 tokens and more.
-        self.sketch_grouped_words = (
-            repack_sketch_grouped(codes, 2 * i, h) if max_tokens >= GROUPED_SCREEN_MIN_TOKENS else None
-        )
-        self.sketch_codes = codes if retain_reference_sketch else None
         self.sketch_resident_bytes = (
             self.sketch_words.numel() * 4
             + statistics.numel() * 2

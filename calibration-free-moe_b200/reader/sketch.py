@@ -257,3 +257,66 @@ def repack_sketch_grouped(codes: Tensor, rows: int, hidden: int) -> Tensor:
         word = (grouped << shifts).sum(-1)
         out[expert] = torch.where(word >= 2**31, word - 2**32, word).to(torch.int32)
     return out
+
+
+def build_sketch_on_device(weights: Tensor, signs: Tensor) -> tuple[Tensor, Tensor, Tensor]:
+    """The sketch of CUDA gate/up rows `[E, 2 I, H]`, built by the library's kernel.
+
+    Returns `(words, grouped_words, statistics)`: the two kernel layouts
+    (`repack_sketch` and `repack_sketch_grouped` of the reference-layout codes) and
+    the FP16 statistics (logical `[E, 2 I, B, 2]` over physical `[E, B, 2, 2 I]`),
+    without the reference-layout codes in between: one pass over the weights, a
+    few milliseconds per layer instead of seconds.  Rotation and rule are those of
+    `build_sketch`; the block sums are added in another order, so single
+    coordinates within rounding of the threshold may differ from it
+    (`codes_from_words` gives the reference-layout codes of the result).
+    """
+    import ctypes
+
+    from .. import _native
+
+    experts, rows, hidden = weights.shape
+    if (not weights.is_cuda or weights.dtype != torch.bfloat16 or not weights.is_contiguous()
+            or hidden % ROTATION_BLOCK or rows % (2 * WORD_ROWS)):
+        raise ValueError("Expected contiguous CUDA BF16 gate/up rows [E, 2I, H], H % 128 == 0, I % 16 == 0")
+    device = weights.device
+    blocks = hidden // ROTATION_BLOCK
+    words = torch.empty((experts, hidden, rows // WORD_ROWS), device=device, dtype=torch.int32)
+    grouped = torch.empty((experts, blocks, rows, 8), device=device, dtype=torch.int32)
+    physical = torch.empty((experts, blocks, 2, rows), device=device, dtype=torch.float16)
+    layer = _native.Layer()
+    layer.hidden, layer.width, layer.experts = hidden, rows // 2, experts
+    signs = signs.to(device=device, dtype=torch.int8).contiguous()
+    with torch.cuda.device(device):
+        code = _native.load().cfm_build_sketch(
+            ctypes.byref(layer), weights.data_ptr(), signs.data_ptr(), words.data_ptr(),
+            grouped.data_ptr(), physical.data_ptr(),
+            ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream),
+        )
+    _native.check(code, "cfm_build_sketch")
+    return words, grouped, physical.permute(0, 3, 1, 2)
+
+
+def codes_from_words(words: Tensor, rows: int, hidden: int) -> Tensor:
+    """Reference-layout codes (as `build_sketch` returns them) of a coordinate-major sketch.
+
+    `words` int32 `[E, H, rows / 16]`.  One expert at a time.
+    """
+    experts = words.shape[0]
+    width = rows // 2
+    groups = (width + 4) // 5
+    device = words.device
+    codes = torch.full((experts, sketch_storage_bytes(rows, hidden)), ZERO_BYTE, device=device,
+                       dtype=torch.uint8)
+    offsets = _code_offsets(rows, hidden, device)[:, : 2 * groups].reshape(-1)
+    place = torch.tensor([1, 3, 9, 27, 81], device=device, dtype=torch.int16)
+    shifts = 2 * torch.arange(WORD_ROWS, device=device, dtype=torch.int64)
+    for expert in range(experts):
+        unsigned = words[expert].to(torch.int64) & 0xFFFFFFFF
+        digits = ((unsigned.unsqueeze(-1) >> shifts) & 3).reshape(hidden, rows).to(torch.int16)
+        digits = digits.reshape(hidden, 2, width)
+        if groups * 5 != width:
+            digits = torch.nn.functional.pad(digits, (0, groups * 5 - width), value=1)
+        packed = (digits.reshape(hidden, 2, groups, 5) * place).sum(-1)
+        codes[expert, offsets] = packed.permute(0, 2, 1).reshape(-1).to(torch.uint8)
+    return codes

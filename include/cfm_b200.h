@@ -1,10 +1,11 @@
 /*
  * C ABI of the B200 (sm_100a) sparse MoE decode reader.
  *
- * Every entry point takes plain device pointers, sizes and a CUDA stream,
- * enqueues work on that stream and returns without synchronising.  Nothing
- * here allocates device memory: the caller owns weights, sketch, workspace and
- * outputs.  Return value 0 is success, a negative value is one of the
+ * Every per-call entry point takes plain device pointers, sizes and a CUDA
+ * stream, enqueues work on that stream and returns without synchronising, and
+ * allocates no device memory: the caller owns weights, sketch, workspace and
+ * outputs.  (The set-up calls of the peer-memory exchange, cfm_peer_*, are the
+ * exception and say so.)  Return value 0 is success, a negative value is one of the
  * CFM_E_* argument errors (nothing was launched), a positive value is a
  * cudaError_t from a launch.  The host-side Python operator
  * (`ProgressiveReader`) is the only intended caller; it raises ValueError
@@ -179,6 +180,17 @@ const char* cfm_error_string(int code);
 int cfm_workspace_layout_for(const cfm_layer* layer, int32_t capacity,
                              cfm_workspace_layout* layout);
 
+/* Construction: the ternary sketch of the native gate/up rows (`gate_up` bf16
+ * [E, 2I, H], `signs` int8 [H]) written straight into the two kernel layouts
+ * (`sketch`, `sketch_grouped`) and the FP16 statistics (physical [E, B, 2, 2I]).
+ * Reads only hidden, width and experts of `layer`.  Same rotation and rule as the
+ * reference builder; its three FP32 sums per block are added in another order,
+ * so a coordinate within rounding of the threshold, or the last FP16 bit of a
+ * scale, can differ from the reference builder's output.
+ * Replaces: build_sketch (reader/sketch.py:84-150) for construction on the GPU. */
+int cfm_build_sketch(const cfm_layer* layer, const void* gate_up, const int8_t* signs,
+                     uint32_t* sketch, uint32_t* sketch_grouped, void* statistics, void* stream);
+
 /* Input rotation: BF16 rows -> sign flip, 128-point Hadamard butterfly, keep
  * the KEEP largest |v| per block (ties to the lower coordinate), fixed-point
  * copy of the kept values.  Replaces: _prepare_input / _rotate_sketch_block
@@ -215,26 +227,39 @@ int cfm_score(const cfm_layer* layer, void* workspace, int32_t capacity,
 
 /* Select: per token the F best scores, ties to the lower candidate index;
  * writes selected, candidate_ids, counts, starts, tile_starts and adds the
- * call's read-cost counters.  Replaces: _select (progressive.py:1584-1775),
- * _account_fixed (:242-276), _count_reads (:2114-2317). */
+ * call's read-cost counters.  When the pairs are grouped by expert (cfm_route of
+ * a batch of eight tokens and more) it also leaves the list of the call's down
+ * tiles in expert order that cfm_down then reads (cfm_reader_forward builds that
+ * list on its side stream beside the exact gather).  Replaces: _select
+ * (progressive.py:1584-1775), _account_fixed (:242-276), _count_reads
+ * (:2114-2317). */
 int cfm_select(const cfm_layer* layer, void* workspace, int32_t capacity,
                const cfm_call* call, void* stream);
 
 /* Exact gate/up: native BF16 rows of the kept candidates against the input,
- * FP32 accumulation, phi(g) u with the reference's BF16 rounding points.
- * Replaces: _acquire with END == H (progressive.py:1372-1581). */
+ * FP32 accumulation, phi(g) u with the reference's BF16 rounding points.  With
+ * the pairs grouped by expert, the (token, expert) pairs are walked in expert
+ * order, so a row several tokens of one expert kept is fetched from HBM once
+ * (row engine "per token"), or each expert's union of kept rows is read once and
+ * applied to all its tokens (row engine "expert major").  Same bits either way.
+ * Replaces: _acquire with END == H (progressive.py:1372-1581), _group_union
+ * (:2609-2652), _group_complete (:2655-2718). */
 int cfm_exact(const cfm_layer* layer, void* workspace, int32_t capacity,
               const cfm_call* call, void* stream);
 
 /* Down: channel-major down rows of the kept candidates, weighted by their
- * activations, FP32 partial sums per tile of 128 kept rows.
- * Replaces: _down (progressive.py:1778-1856). */
+ * activations, FP32 partial sums per tile of 64 kept rows (per token, tiles in
+ * expert order when the pairs are grouped) or per (token, slot, channel range)
+ * with the expert's union of kept rows read once (row engine "expert major").
+ * Replaces: _down (progressive.py:1778-1856), _group_down (:2721-2801). */
 int cfm_down(const cfm_layer* layer, void* workspace, int32_t capacity,
              const cfm_call* call, void* stream);
 
 /* Recovery encode: sketch features of the skipped channels through the
- * encoder rows, then the router-weighted latent.  Replaces: _encode and
- * _latent (progressive.py:1859-2016). */
+ * encoder rows, then the router-weighted latent; per (token, expert) pair, or
+ * with an expert's encoder rows read once for all its tokens (row engine "expert
+ * major"; same bits).  Replaces: _encode and _latent (progressive.py:1859-2016),
+ * _group_encode (:2804-2865). */
 int cfm_encode(const cfm_layer* layer, void* workspace, int32_t capacity,
                const cfm_call* call, void* stream);
 

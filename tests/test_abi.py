@@ -80,3 +80,33 @@ def test_layout_rejects_bad_dimensions(library):
     assert library.cfm_workspace_layout_for(ctypes.byref(layer), 0, ctypes.byref(layout)) == -3
     layer.hidden = 2000  # not a multiple of the rotation block
     assert library.cfm_workspace_layout_for(ctypes.byref(layer), 64, ctypes.byref(layout)) == -2
+
+
+def test_struct_sizes_match_the_header(library):
+    """The ctypes mirrors have the sizes the C structs of the header have on this ABI."""
+    pointer = ctypes.sizeof(ctypes.c_void_p)
+    assert ctypes.sizeof(_native.Layer) == 14 * 4 + 13 * pointer
+    assert ctypes.sizeof(_native.Call) == 6 * 4 + 7 * pointer
+    assert ctypes.sizeof(_native.Exchange) == 4 * 4 + _native.MAX_RANKS * pointer
+    assert ctypes.sizeof(_native.StaticScreen) == 2 * 4 + 8 * pointer
+    text = HEADER.read_text()
+    assert int(re.search(r"#define\s+CFM_MAX_RANKS\s+(\d+)", text).group(1)) == _native.MAX_RANKS
+    assert (int(re.search(r"#define\s+CFM_PEER_HANDLE_BYTES\s+(\d+)", text).group(1))
+            == _native.PEER_HANDLE_BYTES)
+
+
+def test_exchange_bytes_is_a_host_computation(library):
+    plan = compile_budget(hidden_size=2048, expert_width=768, top_k=8,
+                          retention=0.123046875, screen_keep=0.625)
+    layer = _dimension_layer(plan, 16, 0)
+    size = library.cfm_exchange_bytes(ctypes.byref(layer), 8, 64)
+    # header, lists i32 [P][T][F], rows f32 [P][T][H]
+    assert size == 1024 + 8 * 64 * 756 * 4 + 8 * 64 * 2048 * 4
+    assert library.cfm_exchange_bytes(ctypes.byref(layer), 17, 64) == 0  # more ranks than supported
+
+
+def test_layout_rejects_more_candidates_than_the_selection_takes(library):
+    plan = compile_budget(hidden_size=256, expert_width=4096, top_k=8, retention=0.125,
+                          screen_keep=0.625)
+    with pytest.raises(ValueError):
+        _native.workspace_layout(_dimension_layer(plan, 8, 0), 4)  # N = 32768
