@@ -717,9 +717,7 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 
 #include "cfm_build.cuh"
 
-constexpr int kGroupWarps = 8;                   // 16 sketch rows per warp
-constexpr int kGroupRows = kGroupWarps * 16;     // rows per CTA
-constexpr int kGroupThreads = kGroupWarps * 32;
+constexpr int kGroupWarps = 8;  // 16 sketch rows per warp (default CTA shape)
 
 // m16n8k32 int8 MMA whose accumulator starts at zero.
 __device__ __forceinline__ void mma_s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -749,7 +747,9 @@ struct GroupFetch {
 // lane and digit).  The next block's words, digits, scales and exponents are
 // in flight in registers while the current block computes.  Experts with more
 // than eight tokens take further passes of eight, spread over grid.z.
-__global__ void __launch_bounds__(kGroupThreads, 2) k_screen_grouped(Layer L, Workspace ws) {
+template <int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_screen_grouped(Layer L, Workspace ws) {
+  constexpr int kGroupRows = WARPS * 16;  // rows per CTA
   const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int first = ws.group_offsets[e], total = ws.group_offsets[e + 1] - first;
@@ -1148,6 +1148,8 @@ __global__ void __launch_bounds__(tc::kThreads) k_screen_tc(Layer L, Workspace w
   }
 }
 
+#include "cfm_staged.cuh"
+
 // grid (T, ceil(N / 256)), 256 threads: zero the projections of remote or padded
 // slots (the grouped screen writes only live pairs).
 __global__ void k_clear_dead(Layer L, Workspace ws, const uint8_t* padding) {
@@ -1277,7 +1279,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
                                                            int scores_ready, int row_offset) {
   extern __shared__ uint32_t keys[];
   __shared__ int hist[2048];
-  __shared__ int warp_above[32], warp_ties[32];
+  __shared__ int warp_above[33], warp_ties[32];
   __shared__ int s_digit, s_remaining;
   __shared__ int s_starts[33], s_tie_start[33], s_budget[32];
   const int t = blockIdx.x + row_offset, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -1385,22 +1387,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
   int32_t* cuts = ws.cuts + static_cast<size_t>(t) * (K + 1);
   if (cut_given) cut = static_cast<uint32_t>(cuts[0]);
   auto block_exclusive = [&](int value, int* total) {
-    int scan = value;
-#pragma unroll
-    for (int w = 1; w < 32; w <<= 1) {
-      const int o = __shfl_up_sync(kFull, scan, w);
-      if (lane >= w) scan += o;
-    }
-    __syncthreads();  // previous use of warp_above is over
-    if (lane == 31) warp_above[warp] = scan;
-    __syncthreads();
-    int before = scan - value, sum = 0;
-    for (int w = 0; w < 32; ++w) {
-      if (w < warp) before += warp_above[w];
-      sum += warp_above[w];
-    }
-    *total = sum;
-    return before;
+    return block_exclusive_scan(value, warp_above, total);
   };
   // Counts above the cut and tied with it, packed into one scan (N < 65536).
   const bool budgets = cut_given || cut_only;
@@ -2226,7 +2213,17 @@ static int run_screen_grouped(const Bound& b) {
   // their passes of eight tokens over grid.z.
   const int64_t per_expert = (static_cast<int64_t>(b.T) * b.L.K + b.L.E - 1) / b.L.E;
   const int passes = static_cast<int>(std::min<int64_t>(8, std::max<int64_t>(1, (per_expert + 7) / 8)));
-  const dim3 grid((2 * b.L.I + kGroupRows - 1) / kGroupRows, b.L.E, passes);
+  static const int warps = [] {
+    const char* v = std::getenv("CFM_GROUP_WARPS");
+    const int w = v ? std::atoi(v) : kGroupWarps;
+    return w == 2 || w == 4 ? w : kGroupWarps;
+  }();
+  static const bool staged_screen = [] {
+    const char* v = std::getenv("CFM_SCREEN_STAGED");
+    return !v || std::atoi(v) != 0;
+  }();
+  const int group_rows = warps * 16;
+  const dim3 grid((2 * b.L.I + group_rows - 1) / group_rows, b.L.E, passes);
   const size_t tc_bytes = tc::shared_bytes(b.L.B);
   if (b.L.tensor_engine == CFM_ENGINE_TCGEN05 && tc_bytes <= 200 * 1024) {
     const cudaError_t err = cudaFuncSetAttribute(
@@ -2235,8 +2232,18 @@ static int run_screen_grouped(const Bound& b) {
     const int tc_passes = static_cast<int>(
         std::min<int64_t>(8, std::max<int64_t>(1, (per_expert + tc::kTokens - 1) / tc::kTokens)));
     k_screen_tc<<<dim3(grid.x, grid.y, tc_passes), tc::kThreads, tc_bytes, b.stream>>>(b.L, b.ws);
+  } else if (staged_screen && warps == kGroupWarps &&
+             (reinterpret_cast<uintptr_t>(b.L.sketch_grouped) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(b.L.statistics) & 15) == 0) {
+    const cudaError_t err =
+        cudaFuncSetAttribute(k_screen_staged, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(staged::kSharedBytes));
+    if (err != cudaSuccess) return static_cast<int>(err);
+    k_screen_staged<<<grid, staged::kThreads, staged::kSharedBytes, b.stream>>>(b.L, b.ws);
   } else {
-    k_screen_grouped<<<grid, kGroupThreads, 0, b.stream>>>(b.L, b.ws);
+    if (warps == 2) k_screen_grouped<2><<<grid, 64, 0, b.stream>>>(b.L, b.ws);
+    else if (warps == 4) k_screen_grouped<4><<<grid, 128, 0, b.stream>>>(b.L, b.ws);
+    else k_screen_grouped<8><<<grid, 256, 0, b.stream>>>(b.L, b.ws);
   }
   if ((rc = launched())) return rc;
   if (b.padding || b.L.expert_map) {

@@ -3,9 +3,9 @@
 At these sizes the checks are the properties that do not need a stored answer:
 kept lists are the F best scores in ascending candidate order; every token's
 selection is the same whichever kernel path its batch size picks (one large
-batch, smaller batches, single tokens); outputs of the expert-major path (batches
-of eight tokens and more) and of the per-token path agree within the reference's
-own tolerance between its two paths (rtol 0.016, atol 2e-3,
+batch, smaller batches, single tokens); outputs of the expert-major row engine
+and of the per-token row engine agree within the reference's own tolerance
+between its two paths (rtol 0.016, atol 2e-3,
 tests/test_progressive_reader.py:875-978 of the reference); and a sample of
 tokens is compared with the oracle like the small cases are (projections, scores
 and kept ids bit-exact, output within 1e-2 relative L2 of the FP32 evaluation).
