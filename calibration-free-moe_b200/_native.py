@@ -17,7 +17,7 @@ PACKAGE = Path(__file__).resolve().parent
 SOURCES = [PACKAGE / "csrc" / "cfm_reader.cu"]
 HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE / "csrc" / "cfm_grouped.cuh",
            PACKAGE / "csrc" / "cfm_exchange.cuh", PACKAGE / "csrc" / "cfm_select.cuh",
-           PACKAGE / "csrc" / "cfm_build.cuh", PACKAGE / "csrc" / "cfm_staged.cuh",
+           PACKAGE / "csrc" / "cfm_build.cuh", PACKAGE / "csrc" / "cfm_screen_rows32.cuh",
            PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
 ABI_VERSION = 9

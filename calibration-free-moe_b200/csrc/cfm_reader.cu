@@ -717,7 +717,7 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
 
 #include "cfm_build.cuh"
 
-constexpr int kGroupWarps = 8;  // 16 sketch rows per warp (default CTA shape)
+constexpr int kGroupWarps = 8;  // 16 sketch rows per warp
 
 // m16n8k32 int8 MMA whose accumulator starts at zero.
 __device__ __forceinline__ void mma_s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -747,9 +747,8 @@ struct GroupFetch {
 // lane and digit).  The next block's words, digits, scales and exponents are
 // in flight in registers while the current block computes.  Experts with more
 // than eight tokens take further passes of eight, spread over grid.z.
-template <int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, 16 / WARPS) k_screen_grouped(Layer L, Workspace ws) {
-  constexpr int kGroupRows = WARPS * 16;  // rows per CTA
+__global__ void __launch_bounds__(kGroupWarps * 32, 2) k_screen_grouped(Layer L, Workspace ws) {
+  constexpr int kGroupRows = kGroupWarps * 16;  // rows per CTA
   const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
   const int first = ws.group_offsets[e], total = ws.group_offsets[e + 1] - first;
@@ -1148,7 +1147,7 @@ __global__ void __launch_bounds__(tc::kThreads) k_screen_tc(Layer L, Workspace w
   }
 }
 
-#include "cfm_staged.cuh"
+#include "cfm_screen_rows32.cuh"
 
 // grid (T, ceil(N / 256)), 256 threads: zero the projections of remote or padded
 // slots (the grouped screen writes only live pairs).
@@ -2213,17 +2212,7 @@ static int run_screen_grouped(const Bound& b) {
   // their passes of eight tokens over grid.z.
   const int64_t per_expert = (static_cast<int64_t>(b.T) * b.L.K + b.L.E - 1) / b.L.E;
   const int passes = static_cast<int>(std::min<int64_t>(8, std::max<int64_t>(1, (per_expert + 7) / 8)));
-  static const int warps = [] {
-    const char* v = std::getenv("CFM_GROUP_WARPS");
-    const int w = v ? std::atoi(v) : kGroupWarps;
-    return w == 2 || w == 4 ? w : kGroupWarps;
-  }();
-  static const bool staged_screen = [] {
-    const char* v = std::getenv("CFM_SCREEN_STAGED");
-    return !v || std::atoi(v) != 0;
-  }();
-  const int group_rows = warps * 16;
-  const dim3 grid((2 * b.L.I + group_rows - 1) / group_rows, b.L.E, passes);
+  const dim3 grid((2 * b.L.I + kGroupWarps * 16 - 1) / (kGroupWarps * 16), b.L.E, passes);
   const size_t tc_bytes = tc::shared_bytes(b.L.B);
   if (b.L.tensor_engine == CFM_ENGINE_TCGEN05 && tc_bytes <= 200 * 1024) {
     const cudaError_t err = cudaFuncSetAttribute(
@@ -2232,18 +2221,18 @@ static int run_screen_grouped(const Bound& b) {
     const int tc_passes = static_cast<int>(
         std::min<int64_t>(8, std::max<int64_t>(1, (per_expert + tc::kTokens - 1) / tc::kTokens)));
     k_screen_tc<<<dim3(grid.x, grid.y, tc_passes), tc::kThreads, tc_bytes, b.stream>>>(b.L, b.ws);
-  } else if (staged_screen && warps == kGroupWarps &&
-             (reinterpret_cast<uintptr_t>(b.L.sketch_grouped) & 15) == 0 &&
+  } else if (per_expert < 8 && (reinterpret_cast<uintptr_t>(b.L.sketch_grouped) & 15) == 0 &&
              (reinterpret_cast<uintptr_t>(b.L.statistics) & 15) == 0) {
-    const cudaError_t err =
-        cudaFuncSetAttribute(k_screen_staged, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(staged::kSharedBytes));
-    if (err != cudaSuccess) return static_cast<int>(err);
-    k_screen_staged<<<grid, staged::kThreads, staged::kSharedBytes, b.stream>>>(b.L, b.ws);
+    // Up to eight tokens per expert on average (one pass for most experts): two row
+    // tiles per warp share the digit fragments.  Measured on the benchmark shapes
+    // against the one-tile kernel: 61 vs 67 us (128 experts of width 768, 64 tokens),
+    // 157 vs 257 us (hidden 4096, width 1536, 32 tokens); with eight and more tokens
+    // per expert (256 experts of width 512, 256 tokens) the one-tile kernel, which
+    // has the digits of the next block in registers, is ahead (214 vs 231 us).
+    const dim3 wide((2 * b.L.I + kRows32Warps * 32 - 1) / (kRows32Warps * 32), b.L.E, passes);
+    k_screen_rows32<<<wide, kRows32Warps * 32, 0, b.stream>>>(b.L, b.ws);
   } else {
-    if (warps == 2) k_screen_grouped<2><<<grid, 64, 0, b.stream>>>(b.L, b.ws);
-    else if (warps == 4) k_screen_grouped<4><<<grid, 128, 0, b.stream>>>(b.L, b.ws);
-    else k_screen_grouped<8><<<grid, 256, 0, b.stream>>>(b.L, b.ws);
+    k_screen_grouped<<<grid, kGroupWarps * 32, 0, b.stream>>>(b.L, b.ws);
   }
   if ((rc = launched())) return rc;
   if (b.padding || b.L.expert_map) {
