@@ -1495,51 +1495,68 @@ constexpr int kExactWarps = 4;
 // One warp's dot products of a gate row and an up row with the input staged in
 // shared memory (`xs`, `chunks` 16-byte pieces): eight pieces of each row in
 // flight per lane (2048 columns per sweep), FP32 FMAs in a fixed order, then a
-// butterfly over the lanes.  Every lane returns the sums.
+// butterfly over the lanes.  Every lane returns the sums.  The loads of a sweep and
+// the arithmetic on them are separate steps, so that a kernel can issue a row's
+// first sweep before the barrier that publishes `xs`.
+constexpr int kExactSweep = 8;  // 16-byte pieces of each row per lane and sweep
+
+__device__ __forceinline__ void exact_load(const uint4* gate, const uint4* up, int base, int chunks,
+                                           uint4 (&gw)[kExactSweep], uint4 (&uw)[kExactSweep]) {
+  if (base + 32 * (kExactSweep - 1) < chunks) {
+#pragma unroll
+    for (int k = 0; k < kExactSweep; ++k) {
+      gw[k] = load_stream16(gate + base + 32 * k);
+      uw[k] = load_stream16(up + base + 32 * k);
+    }
+  } else {
+#pragma unroll
+    for (int k = 0; k < kExactSweep; ++k) {
+      const int i = base + 32 * k;
+      gw[k] = uw[k] = make_uint4(0, 0, 0, 0);
+      if (i < chunks) {
+        gw[k] = load_stream16(gate + i);
+        uw[k] = load_stream16(up + i);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void exact_consume(const uint4 (&gw)[kExactSweep],
+                                              const uint4 (&uw)[kExactSweep], const uint4* xs,
+                                              int base, int chunks, float& g, float& u) {
+#pragma unroll
+  for (int k = 0; k < kExactSweep; ++k) {
+    const int i = min(base + 32 * k, chunks - 1);
+    const uint4 xw = xs[i];
+    g = fmaf(bf16_lo(gw[k].x), bf16_lo(xw.x), g);
+    g = fmaf(bf16_hi(gw[k].x), bf16_hi(xw.x), g);
+    g = fmaf(bf16_lo(gw[k].y), bf16_lo(xw.y), g);
+    g = fmaf(bf16_hi(gw[k].y), bf16_hi(xw.y), g);
+    g = fmaf(bf16_lo(gw[k].z), bf16_lo(xw.z), g);
+    g = fmaf(bf16_hi(gw[k].z), bf16_hi(xw.z), g);
+    g = fmaf(bf16_lo(gw[k].w), bf16_lo(xw.w), g);
+    g = fmaf(bf16_hi(gw[k].w), bf16_hi(xw.w), g);
+    u = fmaf(bf16_lo(uw[k].x), bf16_lo(xw.x), u);
+    u = fmaf(bf16_hi(uw[k].x), bf16_hi(xw.x), u);
+    u = fmaf(bf16_lo(uw[k].y), bf16_lo(xw.y), u);
+    u = fmaf(bf16_hi(uw[k].y), bf16_hi(xw.y), u);
+    u = fmaf(bf16_lo(uw[k].z), bf16_lo(xw.z), u);
+    u = fmaf(bf16_hi(uw[k].z), bf16_hi(xw.z), u);
+    u = fmaf(bf16_lo(uw[k].w), bf16_lo(xw.w), u);
+    u = fmaf(bf16_hi(uw[k].w), bf16_hi(xw.w), u);
+  }
+}
+
+// The rest of a row pair whose first sweep (`gw`, `uw`) is loaded already when
+// `loaded`, else the whole pair; same order of operations either way.
 __device__ __forceinline__ void exact_dot(const uint4* gate, const uint4* up, const uint4* xs,
-                                          int chunks, int lane, float& g_out, float& u_out) {
+                                          int chunks, int lane, bool loaded,
+                                          uint4 (&gw)[kExactSweep], uint4 (&uw)[kExactSweep],
+                                          float& g_out, float& u_out) {
   float g = 0.0f, u = 0.0f;
-  constexpr int U = 8;
-  for (int base = lane; base < chunks; base += 32 * U) {
-    uint4 gw[U], uw[U];
-    if (base + 32 * (U - 1) < chunks) {
-#pragma unroll
-      for (int k = 0; k < U; ++k) {
-        gw[k] = load_stream16(gate + base + 32 * k);
-        uw[k] = load_stream16(up + base + 32 * k);
-      }
-    } else {
-#pragma unroll
-      for (int k = 0; k < U; ++k) {
-        const int i = base + 32 * k;
-        gw[k] = uw[k] = make_uint4(0, 0, 0, 0);
-        if (i < chunks) {
-          gw[k] = load_stream16(gate + i);
-          uw[k] = load_stream16(up + i);
-        }
-      }
-    }
-#pragma unroll
-    for (int k = 0; k < U; ++k) {
-      const int i = min(base + 32 * k, chunks - 1);
-      const uint4 xw = xs[i];
-      g = fmaf(bf16_lo(gw[k].x), bf16_lo(xw.x), g);
-      g = fmaf(bf16_hi(gw[k].x), bf16_hi(xw.x), g);
-      g = fmaf(bf16_lo(gw[k].y), bf16_lo(xw.y), g);
-      g = fmaf(bf16_hi(gw[k].y), bf16_hi(xw.y), g);
-      g = fmaf(bf16_lo(gw[k].z), bf16_lo(xw.z), g);
-      g = fmaf(bf16_hi(gw[k].z), bf16_hi(xw.z), g);
-      g = fmaf(bf16_lo(gw[k].w), bf16_lo(xw.w), g);
-      g = fmaf(bf16_hi(gw[k].w), bf16_hi(xw.w), g);
-      u = fmaf(bf16_lo(uw[k].x), bf16_lo(xw.x), u);
-      u = fmaf(bf16_hi(uw[k].x), bf16_hi(xw.x), u);
-      u = fmaf(bf16_lo(uw[k].y), bf16_lo(xw.y), u);
-      u = fmaf(bf16_hi(uw[k].y), bf16_hi(xw.y), u);
-      u = fmaf(bf16_lo(uw[k].z), bf16_lo(xw.z), u);
-      u = fmaf(bf16_hi(uw[k].z), bf16_hi(xw.z), u);
-      u = fmaf(bf16_lo(uw[k].w), bf16_lo(xw.w), u);
-      u = fmaf(bf16_hi(uw[k].w), bf16_hi(xw.w), u);
-    }
+  for (int base = lane; base < chunks; base += 32 * kExactSweep) {
+    if (!(loaded && base == lane)) exact_load(gate, up, base, chunks, gw, uw);
+    exact_consume(gw, uw, xs, base, chunks, g, u);
   }
 #pragma unroll
   for (int w = 16; w; w >>= 1) {
@@ -1575,20 +1592,32 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
     }
   }
   const int chunks = L.H / 8;
+  const size_t up_offset = static_cast<size_t>(L.I) * L.H / 8;
+  // The rows of a candidate of a local expert, or null.
+  auto rows_of = [&](int index) -> const uint4* {
+    if (index >= L.F) return nullptr;
+    const int cid = list[index];
+    if (cid < 0) return nullptr;
+    const int slot = cid / L.I, c = cid - slot * L.I;
+    const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
+    if (e < 0) return nullptr;
+    return reinterpret_cast<const uint4*>(L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
+  };
+  // The first row pair's first sweep is on its way while the input row is staged.
+  const int first = blockIdx.x * kExactWarps + warp;
+  uint4 gw[kExactSweep], uw[kExactSweep];
+  const uint4* first_rows = rows_of(first);
+  if (first_rows) exact_load(first_rows, first_rows + up_offset, lane, chunks, gw, uw);
   const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
   for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
   __syncthreads();
-  for (int index = blockIdx.x * kExactWarps + warp; index < L.F;
-       index += gridDim.x * kExactWarps) {
+  for (int index = first; index < L.F; index += gridDim.x * kExactWarps) {
   const int cid = list[index];
   if (cid < 0) break;  // lists end with -1 entries
-  const int slot = cid / L.I, c = cid - slot * L.I;
-  const int e = ws.ids[static_cast<size_t>(t) * L.K + slot];
-  if (e < 0) continue;
-  const uint4* gate = reinterpret_cast<const uint4*>(
-      L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
+  const uint4* gate = index == first ? first_rows : rows_of(index);
+  if (!gate) continue;
   float g, u;
-  exact_dot(gate, gate + static_cast<size_t>(L.I) * L.H / 8, xs, chunks, lane, g, u);
+  exact_dot(gate, gate + up_offset, xs, chunks, lane, index == first, gw, uw, g, u);
   if (lane == 0) {
     ws.activations[static_cast<size_t>(t) * L.N + cid] =
         __float2bfloat16_rn(exact_feature(g, u, L.activation));
@@ -1616,17 +1645,24 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact_pairs(Layer L, Works
   const int start = ws.starts[pair];
   const int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * L.F + start;
   const int chunks = L.H / 8;
+  const size_t up_offset = static_cast<size_t>(L.I) * L.H / 8;
+  const uint4* expert_rows =
+      reinterpret_cast<const uint4*>(L.gate_up + static_cast<size_t>(e) * 2 * L.I * L.H);
+  // The first row pair's first sweep is on its way while the input row is staged.
+  const int first = blockIdx.x * kExactWarps + warp;
+  uint4 gw[kExactSweep], uw[kExactSweep];
+  if (first < count) {
+    const uint4* gate = expert_rows + static_cast<size_t>(list[first] - slot * L.I) * chunks;
+    exact_load(gate, gate + up_offset, lane, chunks, gw, uw);
+  }
   const uint4* x = reinterpret_cast<const uint4*>(hidden + static_cast<size_t>(t) * L.H);
   for (int i = tid; i < chunks; i += kExactWarps * 32) xs[i] = x[i];
   __syncthreads();
-  for (int index = blockIdx.x * kExactWarps + warp; index < count;
-       index += gridDim.x * kExactWarps) {
+  for (int index = first; index < count; index += gridDim.x * kExactWarps) {
     const int cid = list[index];
-    const int c = cid - slot * L.I;
-    const uint4* gate = reinterpret_cast<const uint4*>(
-        L.gate_up + (static_cast<size_t>(e) * 2 * L.I + c) * L.H);
+    const uint4* gate = expert_rows + static_cast<size_t>(cid - slot * L.I) * chunks;
     float g, u;
-    exact_dot(gate, gate + static_cast<size_t>(L.I) * L.H / 8, xs, chunks, lane, g, u);
+    exact_dot(gate, gate + up_offset, xs, chunks, lane, index == first, gw, uw, g, u);
     if (lane == 0) {
       ws.activations[static_cast<size_t>(t) * L.N + cid] =
           __float2bfloat16_rn(exact_feature(g, u, L.activation));

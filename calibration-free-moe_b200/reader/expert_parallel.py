@@ -452,8 +452,18 @@ class ReplicatedScreenEngine:
         screened = plan.completion_count < plan.candidate_count
         with torch.cuda.device(device):
             if screened:
+                # Routing and the grouping by expert do not depend on the rotated input:
+                # they run on the side stream beside the rotation, as in the whole-layer call.
+                main = torch.cuda.current_stream(device)
+                self._fork.record(main)
+                with torch.cuda.stream(self._side):
+                    self._side.wait_event(self._fork)
+                    self._home_stage("cfm_route", call)
+                    self._join.record(self._side)
                 self._home_stage("cfm_prepare_input", call)
-            self._home_stage("cfm_route", call)
+                main.wait_event(self._join)
+            else:
+                self._home_stage("cfm_route", call)
             self._mark("prepare + route")
             if screened:
                 self._home_stage("cfm_screen", call)
