@@ -327,7 +327,7 @@ def cpu_oracle_rate(shape, plan, tokens: int, seconds: float = 10.0) -> dict:
     reader_oracle.forward(**{**arguments, "hidden": arguments["hidden"][:1],
                              "ids": arguments["ids"][:1], "weights": arguments["weights"][:1]})
     done, elapsed, cores = 0, 0.0, 1
-    while elapsed < seconds and done < 8 * tokens:
+    while elapsed < seconds and done < 64 * tokens:
         start = time.perf_counter()
         cores = reader_oracle.forward(**arguments)["threads"]
         elapsed += time.perf_counter() - start
