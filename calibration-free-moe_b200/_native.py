@@ -20,7 +20,7 @@ HEADERS = [PACKAGE / "csrc" / "cfm_device.cuh", PACKAGE / "csrc" / "cfm_grouped.
            PACKAGE / "csrc" / "cfm_build.cuh", PACKAGE / "csrc" / "cfm_screen_rows32.cuh",
            PACKAGE.parent / "include" / "cfm_b200.h"]
 LIBRARY = PACKAGE / "libcfm_b200.so"
-ABI_VERSION = 9
+ABI_VERSION = 10
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -31,7 +31,7 @@ NVCC_FLAGS = [
 # Entry points include/cfm_b200.h declares; `load()` checks each one resolves.
 STAGES = (
     "cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_score", "cfm_select", "cfm_exact",
-    "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_adopt", "cfm_reader_forward",
+    "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_adopt", "cfm_list_tiles", "cfm_reader_forward",
     "cfm_exchange_send_lists",
 )
 PEER_SYMBOLS = ("cfm_build_sketch", "cfm_exchange_bytes", "cfm_peer_alloc", "cfm_peer_export", "cfm_peer_import",

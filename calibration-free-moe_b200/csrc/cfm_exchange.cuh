@@ -16,7 +16,8 @@
 //                           rank's tokens
 //
 // One layer call is one epoch.  The home rank of a token stores its kept list
-// into every rank's `lists` (k_send_lists); owners wait for the lists they adopt
+// into every rank's `lists` (the tail of k_select when the call carries the
+// exchange, or k_send_lists as a launch of its own); owners wait for the lists they adopt
 // (k_adopt), compute, and store each token's partial output row straight into
 // slot [owner] of the home rank's `rows` (k_partial_output); the home rank waits
 // for all owners' rows and adds them in rank order (k_finish_rows), so the sum

@@ -643,12 +643,8 @@ __global__ void __launch_bounds__(512) k_screen(Layer L, Workspace ws, const uin
 // Lists the active (token, slot) pairs of every local expert.  One CTA; dynamic
 // shared memory: 2 * E counters.  The order of an expert's pairs is whatever the
 // atomics produce; every pair's result is independent of it.
-// With `with_tiles` (the kept counts are already known: the selection was adopted)
-// the CTA goes on to list the call's down tiles (cfm_select.cuh).
-__device__ __forceinline__ void list_down_tiles(const Layer& L, const Workspace& ws, int* scratch);
-
 __global__ void __launch_bounds__(1024) k_group(Layer L, Workspace ws, const uint8_t* padding,
-                                                int T, int with_tiles) {
+                                                int T) {
   extern __shared__ int group_smem[];
   int* count = group_smem;
   int* cursor = group_smem + L.E;
@@ -685,11 +681,6 @@ __global__ void __launch_bounds__(1024) k_group(Layer L, Workspace ws, const uin
     if (e >= 0 && !(padding && padding[p / L.K])) {
       ws.group_pairs[atomicAdd(&cursor[e], 1)] = p;
     }
-  }
-  if (with_tiles) {
-    __threadfence_block();
-    __syncthreads();  // group_offsets and group_pairs are read back below
-    list_down_tiles(L, ws, group_smem);
   }
 }
 
@@ -1273,9 +1264,13 @@ __device__ __forceinline__ void account_reads(const Layer& L, int lane, int loca
 }
 
 // grid (T), 1024 threads, dynamic shared memory: N keys.
+// With `peers` (expert parallelism over peer memory; row_offset 0, T = x.tokens) a
+// CTA ends by storing its token's kept list into slot [rank] of every rank's exchange
+// block; the last CTA to arrive releases each destination's flag with the call's epoch.
 __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws,
                                                            const uint8_t* padding,
-                                                           int scores_ready, int row_offset) {
+                                                           int scores_ready, int row_offset,
+                                                           Exchange x, int peers) {
   extern __shared__ uint32_t keys[];
   __shared__ int hist[2048];
   __shared__ int warp_above[33], warp_ties[32];
@@ -1287,9 +1282,45 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
   int32_t* counts = ws.counts + static_cast<size_t>(t) * K;
   int32_t* starts = ws.starts + static_cast<size_t>(t) * K;
   int32_t* tile_starts = ws.tile_starts + static_cast<size_t>(t) * K;
+  // All threads of the CTA call this once the token's list is complete (or has
+  // nothing to say: a padding row, whose list the owners ignore).
+  auto publish = [&](bool send) {
+    __syncthreads();  // the list is complete in global memory for this CTA's threads
+    uint32_t* header = exchange_header(x, x.rank);
+    const uint32_t epoch = header[kExchangeEpoch] + 1u;
+    if (send) {
+      const int32_t* mine = ws.candidate_ids + static_cast<size_t>(t) * F;
+      const size_t at = (static_cast<size_t>(x.rank) * x.tokens + t) * F;
+      if (F % 4 == 0) {
+        const int quads = F / 4;
+        for (int j = tid; j < x.world * quads; j += kSelectThreads) {
+          const int d = j / quads, i = j - d * quads;
+          int4* out = reinterpret_cast<int4*>(
+              reinterpret_cast<int32_t*>(x.block[d] + exchange_lists_offset()) + at);
+          out[i] = reinterpret_cast<const int4*>(mine)[i];
+        }
+      } else {
+        for (int j = tid; j < x.world * F; j += kSelectThreads) {
+          const int d = j / F, i = j - d * F;
+          (reinterpret_cast<int32_t*>(x.block[d] + exchange_lists_offset()) + at)[i] = mine[i];
+        }
+      }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < x.world) {
+      uint32_t* counter = header + kExchangeListsArrive + tid;
+      if (atomicAdd(counter, 1u) == gridDim.x - 1) {
+        *counter = 0;
+        __threadfence_system();
+        store_release_system(exchange_header(x, tid) + kExchangeListsFlag + x.rank, epoch);
+      }
+    }
+  };
   if (padding && padding[t]) {
     if (tid < K) counts[tid] = starts[tid] = tile_starts[tid] = 0;
     if (tid <= K) ws.cuts[static_cast<size_t>(t) * (K + 1) + tid] = 0;
+    if (peers) publish(false);
     return;
   }
   const bool screened = F < N;
@@ -1485,6 +1516,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
     }
     account_reads(L, lane, local_slots, kept_local, screened);
   }
+  if (peers) publish(true);
 }
 
 // ---------------------------------------------------------------------------
@@ -2225,7 +2257,7 @@ static int run_route(const Bound& b, const cfm_call* call) {
   int rc = launched();
   if (rc || !screens_grouped(b)) return rc;
   // The expert-major screen reads the (token, slot) pairs grouped by expert.
-  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T, 0);
+  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
   return launched();
 }
 
@@ -2314,7 +2346,7 @@ static int run_screen_projections(const Bound& b) {
 
 static bool pairs_grouped(const Bound& b);
 
-static int run_select(const Bound& b, int scores_ready) {
+static int run_select(const Bound& b, int scores_ready, const Exchange* exchange = nullptr) {
   const size_t smem = sizeof(uint32_t) * b.L.N;
   if (smem + 10240 > 48 * 1024) {  // static shared memory counts against the default limit
     const cudaError_t err = cudaFuncSetAttribute(
@@ -2322,7 +2354,8 @@ static int run_select(const Bound& b, int scores_ready) {
     if (err != cudaSuccess) return static_cast<int>(err);
   }
   k_select<<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready,
-                                                    b.row_offset);
+                                                    b.row_offset, exchange ? *exchange : Exchange{},
+                                                    exchange != nullptr);
   return launched();
 }
 
@@ -2574,11 +2607,21 @@ CFM_STAGE(cfm_prepare_input, return run_prepare(b, call);)
 CFM_STAGE(cfm_route, return run_route(b, call);)
 CFM_STAGE(cfm_screen, return run_screen(b);)
 CFM_STAGE(cfm_select, {
-  const int code = run_select(b, call->scores_ready);
+  // With an exchange in the call (home rank of an expert-parallel layer, plain
+  // selection of its own rows) the kernel also sends the kept lists to all ranks.
+  Exchange x = {};
+  const bool send = call->exchange != nullptr && call->scores_ready == 0;
+  if (send) {
+    const int bound = bind_exchange(call->exchange, layer, call->exchange->world * b.T, &x);
+    if (bound) return bound;
+    if (b.row_offset != 0) return CFM_E_CAPACITY;
+  }
+  const int code = run_select(b, call->scores_ready, send ? &x : nullptr);
   // Mode 3 only publishes the cut; every other mode leaves final counts behind.
   return code || call->scores_ready == 3 ? code : run_list_tiles(b);
 })
 CFM_STAGE(cfm_score, return run_score(b);)
+CFM_STAGE(cfm_list_tiles, return run_list_tiles(b);)
 CFM_STAGE(cfm_exact, return run_exact(b, call);)
 CFM_STAGE(cfm_down, return run_down(b);)
 CFM_STAGE(cfm_encode, return run_encode(b);)
@@ -2632,8 +2675,9 @@ int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const c
                                      call->weights_are_bf16, b.padding, call->lists, x, peers);
   int code = launched();
   if (code || !pairs_grouped(b)) return code;
-  // The exact and down kernels read the pairs grouped by expert.
-  k_group<<<1, 1024, sizeof(int) * std::max(2 * b.L.E, 40), b.stream>>>(b.L, b.ws, b.padding, b.T, 1);
+  // The exact and down kernels read the pairs grouped by expert; the down tiles are
+  // listed by cfm_list_tiles, which may run beside cfm_exact.
+  k_group<<<1, 1024, 2 * sizeof(int) * b.L.E, b.stream>>>(b.L, b.ws, b.padding, b.T);
   return launched();
 }
 

@@ -294,6 +294,8 @@ class ShardedScreenEngine:
         # The recovery encoder runs beside the two gathers on its own stream.
         self._side = torch.cuda.Stream(device, priority=-1)
         self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+        self._lister = torch.cuda.Stream(device, priority=-1)
+        self._adopted, self._listed = torch.cuda.Event(), torch.cuda.Event()
 
     def screen(self, hidden, ids, weights, padding):
         reader = self.reader
@@ -424,6 +426,8 @@ class ReplicatedScreenEngine:
         # The recovery encoder runs beside the dispatch and the owners' work on its own stream.
         self._side = torch.cuda.Stream(device, priority=-1)
         self._fork, self._join = torch.cuda.Event(), torch.cuda.Event()
+        self._lister = torch.cuda.Stream(device, priority=-1)
+        self._adopted, self._listed = torch.cuda.Event(), torch.cuda.Event()
         self._library = owner._library
         # Called with a stage name after each stage is enqueued (timelines); None = off.
         self.trace = None
@@ -468,17 +472,18 @@ class ReplicatedScreenEngine:
             if screened:
                 self._home_stage("cfm_screen", call)
             self._mark("screen")
-            self._home_stage("cfm_select", call)
-            self._mark("select")
             if self.exchange is not None:
                 # Every rank brings the same number of rows to a call (as the collectives
                 # require too); the blocks are laid out for that number, up to their capacity.
+                # With the exchange in the call the selection kernel ends by storing each
+                # token's kept list into every rank's block (peer stores) and releasing
+                # the flags.
                 if rows > self.exchange.tokens:
                     raise ValueError("Sparse input exceeds the prepared token/candidate contract")
                 self.exchange.struct.tokens = rows
                 call.exchange = ctypes.addressof(self.exchange.struct)
-                self._home_stage("cfm_exchange_send_lists", call)
-                self._mark("send lists (peer stores)")
+            self._home_stage("cfm_select", call)
+            self._mark("select" + (" + send lists (peer stores)" if self.exchange is not None else ""))
             if home.rank:
                 main = torch.cuda.current_stream(device)
                 self._fork.record(main)
@@ -499,10 +504,23 @@ class ReplicatedScreenEngine:
             call.lists = lists.data_ptr()
         self._serve_keep = (hidden, ids, weights, padding, lists)
         with torch.cuda.device(owner._device):
-            for stage in ("cfm_adopt", "cfm_exact", "cfm_down", "cfm_partial_output"):
-                owner._stage(stage, call)
-                self._mark(stage[4:] + (" (waits for the lists)" if stage == "cfm_adopt"
-                                        and self.exchange is not None else ""))
+            main = torch.cuda.current_stream(owner._device)
+            owner._stage("cfm_adopt", call)
+            self._mark("adopt" + (" (waits for the lists)" if self.exchange is not None else ""))
+            # The exact gather does not read the list of down tiles: one CTA builds it on
+            # a second stream meanwhile.
+            self._adopted.record(main)
+            with torch.cuda.stream(self._lister):
+                self._lister.wait_event(self._adopted)
+                owner._stage("cfm_list_tiles", call)
+                self._listed.record(self._lister)
+            owner._stage("cfm_exact", call)
+            self._mark("exact")
+            main.wait_event(self._listed)
+            owner._stage("cfm_down", call)
+            self._mark("down")
+            owner._stage("cfm_partial_output", call)
+            self._mark("partial_output")
         return self._routed[:rows]
 
     def finish(self, routed):

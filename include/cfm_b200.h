@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define CFM_ABI_VERSION 9
+#define CFM_ABI_VERSION 10
 
 /* argument errors */
 #define CFM_E_NULL -1       /* a required pointer is NULL                      */
@@ -290,16 +290,24 @@ int cfm_finish(const cfm_layer* layer, int32_t tokens, const float* combined,
  * ids; the ranks that own the experts adopt them.  From call->ids, call->weights
  * (as cfm_route) and call->lists this writes the workspace's routing order, the
  * list cut down to the local slots, and their counts, starts and down-tile
- * starts, after which cfm_exact, cfm_down and cfm_partial_output run as usual.
+ * starts, after which cfm_exact, cfm_list_tiles, cfm_down and cfm_partial_output run.
  * No reference counterpart: the reference replicates the tokens and all-reduces
  * the scores instead (progressive.py:4245-4251). */
 int cfm_adopt(const cfm_layer* layer, void* workspace, int32_t capacity, const cfm_call* call,
               void* stream);
 
+/* Lists the down tiles of the call in expert order (batches of eight tokens and
+ * more; nothing to do below that).  cfm_select does this itself; after cfm_adopt the
+ * caller runs it anywhere between cfm_adopt and cfm_down, for instance on a second
+ * stream beside cfm_exact, which does not read the list. */
+int cfm_list_tiles(const cfm_layer* layer, void* workspace, int32_t capacity,
+                   const cfm_call* call, void* stream);
+
 /* Expert parallelism over peer memory (NVLink), replacing the collectives around
- * cfm_adopt and cfm_partial_output.  Per layer call and rank: cfm_exchange_send_lists
- * (home side, after cfm_select) stores the kept lists of this rank's T tokens into
- * every rank's block; cfm_adopt with call->exchange waits for the lists of each
+ * cfm_adopt and cfm_partial_output.  Per layer call and rank: cfm_select with
+ * call->exchange (home side; plain selection, scores_ready 0) ends by storing the
+ * kept lists of this rank's T tokens into every rank's block (cfm_exchange_send_lists
+ * does the same as a launch of its own after a cfm_select without the exchange); cfm_adopt with call->exchange waits for the lists of each
  * row's home rank; cfm_partial_output with call->exchange stores each row's FP32
  * partial sums into the block of the row's home rank; cfm_finish_rows (home side)
  * waits for the rows of all ranks, adds them in rank order, adds the decoder term

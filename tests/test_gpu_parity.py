@@ -473,7 +473,7 @@ def test_owner_side_adopts_a_home_selection_bit_for_bit(name):
     call = owner._call_struct(tokens, hidden, ids, weights, None, routed, False)
     lists = whole.candidate_ids[-1][:tokens].clone()
     call.lists = lists.data_ptr()
-    for stage in ("cfm_adopt", "cfm_exact", "cfm_down", "cfm_partial_output"):
+    for stage in ("cfm_adopt", "cfm_list_tiles", "cfm_exact", "cfm_down", "cfm_partial_output"):
         owner._stage(stage, call)
     out = torch.empty_like(expected)
     code = whole._library.cfm_finish(
