@@ -32,7 +32,6 @@ NVCC_FLAGS = [
 STAGES = (
     "cfm_prepare_input", "cfm_route", "cfm_screen", "cfm_score", "cfm_select", "cfm_exact",
     "cfm_down", "cfm_encode", "cfm_output", "cfm_partial_output", "cfm_adopt", "cfm_list_tiles", "cfm_reader_forward",
-    "cfm_exchange_send_lists",
 )
 PEER_SYMBOLS = ("cfm_build_sketch", "cfm_exchange_bytes", "cfm_peer_alloc", "cfm_peer_export", "cfm_peer_import",
                 "cfm_peer_release", "cfm_exchange_status", "cfm_finish_rows")

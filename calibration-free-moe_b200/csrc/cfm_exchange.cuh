@@ -10,14 +10,14 @@
 //                        [16 + p] lists of rank p have landed for this epoch,
 //                        [32 + p] rows of owner p have landed for this epoch,
 //                        [48 + p], [64 + p] arrival counters of this rank's own
-//                        sending CTAs, per destination
+//                        sending CTAs (lists, rows), per destination
 //   lists    i32 [P][T][F]  kept-channel lists of every rank's tokens
 //   rows     f32 [P][T][H]  per owner rank, its partial output rows of THIS
 //                           rank's tokens
 //
 // One layer call is one epoch.  The home rank of a token stores its kept list
 // into every rank's `lists` (the tail of k_select when the call carries the
-// exchange, or k_send_lists as a launch of its own); owners wait for the lists they adopt
+// exchange); owners wait for the lists they adopt
 // (k_adopt), compute, and store each token's partial output row straight into
 // slot [owner] of the home rank's `rows` (k_partial_output); the home rank waits
 // for all owners' rows and adds them in rank order (k_finish_rows), so the sum
@@ -98,29 +98,6 @@ __device__ __forceinline__ void exchange_announce(uint32_t* counter, unsigned ex
       store_release_system(flag, epoch);
     }
   }
-}
-
-// grid (P, ctas), 256 threads: the kept lists of this rank's T tokens
-// (`candidate_ids` of the home workspace, [T][F]) into slot [rank] of every
-// rank's `lists`, sixteen bytes per store where the row length allows.
-__global__ void __launch_bounds__(256) k_send_lists(Layer L, Workspace ws, Exchange x) {
-  const int destination = blockIdx.x;
-  const uint32_t epoch = exchange_header(x, x.rank)[kExchangeEpoch] + 1u;
-  const size_t count = static_cast<size_t>(x.tokens) * L.F;
-  int32_t* out = reinterpret_cast<int32_t*>(x.block[destination] + exchange_lists_offset()) +
-                 static_cast<size_t>(x.rank) * count;
-  const int32_t* in = ws.candidate_ids;
-  const size_t stride = static_cast<size_t>(gridDim.y) * blockDim.x;
-  const size_t first = static_cast<size_t>(blockIdx.y) * blockDim.x + threadIdx.x;
-  if (count % 4 == 0) {
-    const int4* in4 = reinterpret_cast<const int4*>(in);
-    int4* out4 = reinterpret_cast<int4*>(out);
-    for (size_t i = first; i < count / 4; i += stride) out4[i] = in4[i];
-  } else {
-    for (size_t i = first; i < count; i += stride) out[i] = in[i];
-  }
-  exchange_announce(exchange_header(x, x.rank) + kExchangeListsArrive + destination, gridDim.y,
-                    exchange_header(x, destination) + kExchangeListsFlag + x.rank, epoch);
 }
 
 // grid (H / 128, T), 128 threads: the home rank's output rows.  Waits for the

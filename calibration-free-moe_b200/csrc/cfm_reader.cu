@@ -2740,22 +2740,6 @@ int cfm_exchange_status(const cfm_exchange* exchange, int32_t* status) {
   return static_cast<int>(err);
 }
 
-int cfm_exchange_send_lists(const cfm_layer* layer, void* workspace, int32_t capacity,
-                            const cfm_call* call, void* stream) {
-  Bound b;
-  const int rc = bind_call(layer, workspace, capacity, call, stream, &b);
-  if (rc) return rc;
-  if (!call->exchange) return CFM_E_NULL;
-  Exchange x = {};
-  const int bound = bind_exchange(call->exchange, layer, call->exchange->world * b.T, &x);
-  if (bound) return bound;
-  if (b.T != x.tokens) return CFM_E_CAPACITY;
-  const int64_t pieces = (static_cast<int64_t>(b.T) * b.L.F + 1023) / 1024;
-  const int ctas = static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(32, pieces)));
-  k_send_lists<<<dim3(x.world, ctas), 256, 0, b.stream>>>(b.L, b.ws, x);
-  return launched();
-}
-
 int cfm_finish_rows(const cfm_layer* layer, const cfm_exchange* exchange, const float* latent,
                     void* out, void* stream) {
   if (!layer || !exchange || !out) return CFM_E_NULL;

@@ -306,9 +306,8 @@ int cfm_list_tiles(const cfm_layer* layer, void* workspace, int32_t capacity,
 /* Expert parallelism over peer memory (NVLink), replacing the collectives around
  * cfm_adopt and cfm_partial_output.  Per layer call and rank: cfm_select with
  * call->exchange (home side; plain selection, scores_ready 0) ends by storing the
- * kept lists of this rank's T tokens into every rank's block (cfm_exchange_send_lists
- * does the same as a launch of its own after a cfm_select without the exchange); cfm_adopt with call->exchange waits for the lists of each
- * row's home rank; cfm_partial_output with call->exchange stores each row's FP32
+ * kept lists of this rank's T tokens into every rank's block; cfm_adopt with
+ * call->exchange waits for the lists of each row's home rank; cfm_partial_output with call->exchange stores each row's FP32
  * partial sums into the block of the row's home rank; cfm_finish_rows (home side)
  * waits for the rows of all ranks, adds them in rank order, adds the decoder term
  * of `latent` (f32 [T, R], or NULL) and stores BF16 `out` [T, H].  Every device-side
@@ -326,8 +325,6 @@ int cfm_peer_export(void* block, void* handle);
 int cfm_peer_import(const void* handle, void** block);
 int cfm_peer_release(void* block, int32_t imported);
 int cfm_exchange_status(const cfm_exchange* exchange, int32_t* status);
-int cfm_exchange_send_lists(const cfm_layer* layer, void* workspace, int32_t capacity,
-                            const cfm_call* call, void* stream);
 int cfm_finish_rows(const cfm_layer* layer, const cfm_exchange* exchange, const float* latent,
                     void* out, void* stream);
 

@@ -1,7 +1,7 @@
 """Expert-parallel exchange over peer memory, on one GPU.
 
 The kernels that move the kept lists and the partial output rows between ranks
-(`cfm_exchange_send_lists`, `cfm_adopt` and `cfm_partial_output` with an exchange,
+(`cfm_select`, `cfm_adopt` and `cfm_partial_output` with an exchange,
 `cfm_finish_rows`) run here with a group of one rank: the rank stores into its own
 block, so every flag a kernel waits for has been set by an earlier kernel of the
 same stream and no launch ever waits on another.  Two ranks over NVLink are
