@@ -88,9 +88,11 @@ __device__ __forceinline__ bool exchange_wait(const uint32_t* flag, uint32_t epo
 // (the destination's memory).
 __device__ __forceinline__ void exchange_announce(uint32_t* counter, unsigned expected,
                                                   uint32_t* flag, uint32_t epoch) {
-  __threadfence_system();
+  // The CTA barrier orders every thread's stores before thread 0's system-scope fence,
+  // which is cumulative: one fence per CTA publishes them all.
   __syncthreads();
   if (threadIdx.x == 0) {
+    __threadfence_system();
     const unsigned old = atomicAdd(counter, 1u);
     if (old == expected - 1) {
       *counter = 0;

@@ -1306,9 +1306,11 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
         }
       }
     }
-    __threadfence_system();
+    // The CTA barrier orders every thread's stores before the fences of the few threads
+    // that announce; a system-scope fence is cumulative.
     __syncthreads();
     if (tid < x.world) {
+      __threadfence_system();
       uint32_t* counter = header + kExchangeListsArrive + tid;
       if (atomicAdd(counter, 1u) == gridDim.x - 1) {
         *counter = 0;
