@@ -24,6 +24,7 @@
 #include <algorithm>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 #include <mutex>
 
 namespace cfm {
@@ -1267,10 +1268,17 @@ __device__ __forceinline__ void account_reads(const Layer& L, int lane, int loca
 // With `peers` (expert parallelism over peer memory; row_offset 0, T = x.tokens) a
 // CTA ends by storing its token's kept list into slot [rank] of every rank's exchange
 // block; the last CTA to arrive releases each destination's flag with the call's epoch.
-__global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws,
-                                                           const uint8_t* padding,
-                                                           int scores_ready, int row_offset,
-                                                           Exchange x, int peers) {
+// Without PEERS the exchange argument is a dummy, so that the single-GPU kernel carries
+// neither the parameter block nor the code of the hand-over.
+struct NoExchange {
+  int world, rank, tokens;
+  char* block[1];
+};
+template <bool PEERS>
+__global__ void __launch_bounds__(kSelectThreads)
+    k_select(Layer L, Workspace ws, const uint8_t* padding, int scores_ready, int row_offset,
+             typename std::conditional<PEERS, Exchange, NoExchange>::type x) {
+  constexpr bool peers = PEERS;
   extern __shared__ uint32_t keys[];
   __shared__ int hist[2048];
   __shared__ int warp_above[33], warp_ties[32];
@@ -1285,6 +1293,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
   // All threads of the CTA call this once the token's list is complete (or has
   // nothing to say: a padding row, whose list the owners ignore).
   auto publish = [&](bool send) {
+    if constexpr (PEERS) {
     __syncthreads();  // the list is complete in global memory for this CTA's threads
     uint32_t* header = exchange_header(x, x.rank);
     const uint32_t epoch = header[kExchangeEpoch] + 1u;
@@ -1317,6 +1326,7 @@ __global__ void __launch_bounds__(kSelectThreads) k_select(Layer L, Workspace ws
         __threadfence_system();
         store_release_system(exchange_header(x, tid) + kExchangeListsFlag + x.rank, epoch);
       }
+    }
     }
   };
   if (padding && padding[t]) {
@@ -1710,23 +1720,46 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact_pairs(Layer L, Works
 // down: gathered channel-major down rows
 // ---------------------------------------------------------------------------
 constexpr int kDownColumns = 1024;  // output columns per CTA: 32 accumulators per lane
+constexpr int kDownStages = 4;      // rows in flight per warp (3, 4 and 6 measured alike)
+constexpr int kDownRowBytes = kDownColumns * 2;  // one row's share of a CTA: 2 KiB per warp and row
+constexpr int down_ring_bytes(int stages) { return 4 * stages * kDownRowBytes; }  // per CTA
 
-// grid (ceil(H / 1024), tiles, T), 128 threads.  One CTA sums up to 64 kept rows
-// of one expert, each scaled by its activation, over 1024 output columns.  A warp
-// takes every fourth row of the tile: per row a lane issues four 16-byte loads
-// 512 bytes apart (2 KiB contiguous per warp and row) at immediate offsets from
-// one address, with the next two rows' loads in flight while the current row is
-// accumulated into 32 FP32 registers.  The four warps' sums are added in warp
-// order through shared memory.  Under expert parallelism
-// (STRIDED) fewer CTAs than tiles are launched per token, since a rank owns few
-// of a token's slots; they walk the tiles in strides.
+// 16 bytes global -> shared memory, past L1, completing in the thread's current
+// cp.async group.
+__device__ __forceinline__ void copy_async16(void* shared, const void* global) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   static_cast<uint32_t>(__cvta_generic_to_shared(shared))),
+               "l"(global)
+               : "memory");
+}
+__device__ __forceinline__ void copy_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int PENDING>
+__device__ __forceinline__ void copy_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory");
+}
+
+// grid (ceil(H / 1024), tiles, T), 128 threads, down_ring_bytes(kDownStages) of dynamic
+// shared memory.  One CTA sums up to 64 kept rows of one expert, each scaled by its
+// activation, over 1024 output columns.  A warp takes every fourth row of the
+// tile.  Rows travel through a ring in shared memory, four per warp in flight:
+// per row a lane copies four 16-byte pieces 512 bytes apart (2 KiB contiguous per
+// warp and row) with cp.async and later reads back exactly the pieces it copied,
+// so a lane only ever waits for its own copy groups and the ring needs no barrier.
+// The row is accumulated into 32 FP32 registers per lane in row order; the four
+// warps' sums are added in warp order through shared memory (the ring's, once
+// all copies have landed).  Under expert parallelism (STRIDED) fewer CTAs than
+// tiles are launched per token, since a rank owns few of a token's slots; they
+// walk the tiles in strides.
 // One tile: `rows` (at most 64) kept rows of slot `slot` of token t, an expert-e
 // slot, whose candidate ids start at `list`, summed into down tile `tile`.
 // Called by all 128 threads of a CTA; begins and ends with the shared arrays free.
+template <int STAGES>
 __device__ __forceinline__ void down_tile(const Layer& L, const Workspace& ws, int t, int slot,
                                           int e, int rows, const int32_t* list, int tile,
                                           int* tile_channel, float* tile_activation,
-                                          float (*red)[kDownColumns]) {
+                                          uint8_t* ring) {
   constexpr int CHUNKS = kDownColumns / 256;  // 16-byte pieces per lane and row
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int column0 = blockIdx.x * kDownColumns + lane * 8;  // this lane's first column
@@ -1746,43 +1779,50 @@ __device__ __forceinline__ void down_tile(const Layer& L, const Workspace& ws, i
   for (int j = 0; j < CHUNKS; ++j)
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[j][i] = 0.0f;
-  auto fetch = [&](int r, uint4 (&w)[CHUNKS]) {
-    const __nv_bfloat16* row = base + static_cast<size_t>(tile_channel[r]) * L.H;
+  // This lane's pieces of ring slot s of its warp.
+  uint8_t* mine = ring + warp * (STAGES * kDownRowBytes) + lane * 16;
+  auto fetch = [&](int r, int s) {  // row r of the tile into slot s; one copy group
+    if (r < rows) {
+      const __nv_bfloat16* row = base + static_cast<size_t>(tile_channel[r]) * L.H;
 #pragma unroll
-    for (int j = 0; j < CHUNKS; ++j)
-      w[j] = live[j] ? load_stream16(row + 256 * j) : make_uint4(0, 0, 0, 0);
+      for (int j = 0; j < CHUNKS; ++j)
+        if (live[j]) copy_async16(mine + s * kDownRowBytes + 512 * j, row + 256 * j);
+    }
+    copy_async_commit();  // also when empty: the group count per iteration stays fixed
   };
-  auto add = [&](int r, const uint4 (&w)[CHUNKS]) {
+  auto add = [&](int r, int s) {
     const float a = tile_activation[r];
 #pragma unroll
     for (int j = 0; j < CHUNKS; ++j) {
-      acc[j][0] = fmaf(bf16_lo(w[j].x), a, acc[j][0]);
-      acc[j][1] = fmaf(bf16_hi(w[j].x), a, acc[j][1]);
-      acc[j][2] = fmaf(bf16_lo(w[j].y), a, acc[j][2]);
-      acc[j][3] = fmaf(bf16_hi(w[j].y), a, acc[j][3]);
-      acc[j][4] = fmaf(bf16_lo(w[j].z), a, acc[j][4]);
-      acc[j][5] = fmaf(bf16_hi(w[j].z), a, acc[j][5]);
-      acc[j][6] = fmaf(bf16_lo(w[j].w), a, acc[j][6]);
-      acc[j][7] = fmaf(bf16_hi(w[j].w), a, acc[j][7]);
+      const uint4 w = live[j] ? *reinterpret_cast<const uint4*>(mine + s * kDownRowBytes + 512 * j)
+                              : make_uint4(0, 0, 0, 0);
+      acc[j][0] = fmaf(bf16_lo(w.x), a, acc[j][0]);
+      acc[j][1] = fmaf(bf16_hi(w.x), a, acc[j][1]);
+      acc[j][2] = fmaf(bf16_lo(w.y), a, acc[j][2]);
+      acc[j][3] = fmaf(bf16_hi(w.y), a, acc[j][3]);
+      acc[j][4] = fmaf(bf16_lo(w.z), a, acc[j][4]);
+      acc[j][5] = fmaf(bf16_hi(w.z), a, acc[j][5]);
+      acc[j][6] = fmaf(bf16_lo(w.w), a, acc[j][6]);
+      acc[j][7] = fmaf(bf16_hi(w.w), a, acc[j][7]);
     }
   };
-  // Three row buffers used in turn: two rows' loads fly while one is added.
-  uint4 first_row[CHUNKS], second_row[CHUNKS], third_row[CHUNKS];
-  if (warp < rows) fetch(warp, first_row);
-  if (warp + 4 < rows) fetch(warp + 4, second_row);
-  for (int r = warp; r < rows; r += 12) {
-    if (r + 8 < rows) fetch(r + 8, third_row);
-    add(r, first_row);
-    if (r + 12 < rows) fetch(r + 12, first_row);
-    if (r + 4 < rows) add(r + 4, second_row);
-    if (r + 16 < rows) fetch(r + 16, second_row);
-    if (r + 8 < rows) add(r + 8, third_row);
+#pragma unroll
+  for (int s = 0; s < STAGES; ++s) fetch(warp + 4 * s, s);
+  int s = 0;
+  for (int r = warp; r < rows; r += 4) {
+    copy_async_wait<STAGES - 1>();  // the oldest group, row r, has landed
+    add(r, s);
+    fetch(r + 4 * STAGES, s);  // the slot is free again: its pieces are in registers
+    s = s + 1 == STAGES ? 0 : s + 1;
   }
+  copy_async_wait<0>();
+  __syncthreads();  // every warp is done with the ring: it now holds the warps' sums
+  float(*red)[kDownColumns] = reinterpret_cast<float(*)[kDownColumns]>(ring);
 #pragma unroll
   for (int j = 0; j < CHUNKS; ++j) {
-    float4* mine = reinterpret_cast<float4*>(&red[warp][256 * j + lane * 8]);
-    mine[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
-    mine[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
+    float4* out = reinterpret_cast<float4*>(&red[warp][256 * j + lane * 8]);
+    out[0] = make_float4(acc[j][0], acc[j][1], acc[j][2], acc[j][3]);
+    out[1] = make_float4(acc[j][4], acc[j][5], acc[j][6], acc[j][7]);
   }
   __syncthreads();
   float* parts = ws.down_parts + (static_cast<size_t>(t) * ws.down_tiles + tile) * L.H +
@@ -1801,11 +1841,11 @@ __device__ __forceinline__ void down_tile(const Layer& L, const Workspace& ws, i
   __syncthreads();  // the shared arrays may be reused
 }
 
-template <bool STRIDED>
+template <bool STRIDED, int STAGES>
 __global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const uint8_t* padding) {
+  extern __shared__ __align__(128) uint8_t down_ring[];
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
-  __shared__ __align__(16) float red[4][kDownColumns];
   __shared__ int s_slot, s_first;
   const int t = blockIdx.z, tid = threadIdx.x;
   if (padding && padding[t]) return;
@@ -1836,10 +1876,10 @@ __global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const ui
     __syncthreads();
     const int slot = s_slot, first = s_first;
     if (slot < 0) continue;  // uniform: every thread read the same slot
-    down_tile(L, ws, t, slot, ws.ids[token_pairs + slot],
+    down_tile<STAGES>(L, ws, t, slot, ws.ids[token_pairs + slot],
               min(kDownTileRows, ws.counts[token_pairs + slot] - first),
               ws.candidate_ids + static_cast<size_t>(t) * L.F + ws.starts[token_pairs + slot] + first,
-              tile, tile_channel, tile_activation, red);
+              tile, tile_channel, tile_activation, down_ring);
   } while (STRIDED && (tile += gridDim.y) < used);
 }
 
@@ -1847,15 +1887,16 @@ __global__ void __launch_bounds__(128, 4) k_down(Layer L, Workspace ws, const ui
 // (cfm_select.cuh): grid (ceil(H / 1024), most tiles a call can have), 128
 // threads.  A CTA reads its 32-byte record and goes straight to the tile's rows.
 // Same tiles, same sums, same bits as k_down.
+template <int STAGES>
 __global__ void __launch_bounds__(128, 4) k_down_tiles(Layer L, Workspace ws) {
+  extern __shared__ __align__(128) uint8_t down_ring[];
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
-  __shared__ __align__(16) float red[4][kDownColumns];
   if (static_cast<int>(blockIdx.y) >= ws.tile_count[0]) return;
   const int4* record = reinterpret_cast<const int4*>(ws.tile_list) + 2 * blockIdx.y;
   const int4 a = record[0], b = record[1];  // t, slot, expert, rows | list, tile
-  down_tile(L, ws, a.x, a.y, a.z, a.w, ws.candidate_ids + b.x, b.y, tile_channel,
-            tile_activation, red);
+  down_tile<STAGES>(L, ws, a.x, a.y, a.z, a.w, ws.candidate_ids + b.x, b.y, tile_channel,
+            tile_activation, down_ring);
 }
 
 // ---------------------------------------------------------------------------
@@ -2351,13 +2392,19 @@ static bool pairs_grouped(const Bound& b);
 static int run_select(const Bound& b, int scores_ready, const Exchange* exchange = nullptr) {
   const size_t smem = sizeof(uint32_t) * b.L.N;
   if (smem + 10240 > 48 * 1024) {  // static shared memory counts against the default limit
-    const cudaError_t err = cudaFuncSetAttribute(
-        k_select, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    cudaError_t err = cudaFuncSetAttribute(
+        k_select<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(k_select<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);
   }
-  k_select<<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready,
-                                                    b.row_offset, exchange ? *exchange : Exchange{},
-                                                    exchange != nullptr);
+  if (exchange)
+    k_select<true><<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready,
+                                                            b.row_offset, *exchange);
+  else
+    k_select<false><<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready,
+                                                             b.row_offset, NoExchange{});
   return launched();
 }
 
@@ -2449,6 +2496,12 @@ static int run_exact(const Bound& b, const cfm_call* call) {
   return launched();
 }
 
+// Passes the ring depth of the down kernels to `launch` as a compile-time constant.
+template <typename Launch>
+static int launch_down(Launch launch) {
+  return launch(std::integral_constant<int, kDownStages>{});
+}
+
 static int run_down(const Bound& b) {
   if (!b.L.down) return CFM_E_NULL;
   if (rows_grouped(b)) {
@@ -2467,8 +2520,14 @@ static int run_down(const Bound& b) {
     // The call's tiles were listed in expert order after the selection.
     const int most = b.T * ((b.L.F + kDownTileRows - 1) / kDownTileRows + b.L.K);
     const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, most);
-    k_down_tiles<<<grid, 128, 0, b.stream>>>(b.L, b.ws);
-    return launched();
+    return launch_down([&](auto stages) {
+      constexpr int S = decltype(stages)::value;
+      cudaError_t err = cudaFuncSetAttribute(
+          k_down_tiles<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, down_ring_bytes(S));
+      if (err != cudaSuccess) return static_cast<int>(err);
+      k_down_tiles<S><<<grid, 128, down_ring_bytes(S), b.stream>>>(b.L, b.ws);
+      return launched();
+    });
   }
   int tiles = b.ws.down_tiles;
   if (b.L.expert_map && b.L.global_experts > 0) {
@@ -2478,11 +2537,21 @@ static int run_down(const Bound& b) {
     tiles = static_cast<int>(std::max<int64_t>(2, std::min<int64_t>(tiles, share)));
   }
   const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, tiles, b.T);
-  if (tiles < b.ws.down_tiles)
-    k_down<true><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
-  else
-    k_down<false><<<grid, 128, 0, b.stream>>>(b.L, b.ws, b.padding);
-  return launched();
+  return launch_down([&](auto stages) {
+    constexpr int S = decltype(stages)::value;
+    cudaError_t err = cudaFuncSetAttribute(
+        k_down<true, S>, cudaFuncAttributeMaxDynamicSharedMemorySize, down_ring_bytes(S));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(k_down<false, S>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 down_ring_bytes(S));
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (tiles < b.ws.down_tiles)
+      k_down<true, S><<<grid, 128, down_ring_bytes(S), b.stream>>>(b.L, b.ws, b.padding);
+    else
+      k_down<false, S><<<grid, 128, down_ring_bytes(S), b.stream>>>(b.L, b.ws, b.padding);
+    return launched();
+  });
+
 }
 
 static int run_encode(const Bound& b) {
