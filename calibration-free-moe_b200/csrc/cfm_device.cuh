@@ -142,6 +142,19 @@ __device__ __forceinline__ float bf16_hi(uint32_t w) {
   return __uint_as_float(w & 0xffff0000u);
 }
 
+// Programmatic dependent launch.  A kernel launched with programmatic stream
+// serialisation may start while its predecessor in the stream is still running;
+// grid_dependency_wait() returns once that predecessor has completed and its writes
+// are visible, and must precede the first access to anything the predecessor wrote.
+// grid_dependency_release() lets the successor of the calling grid be scheduled once
+// every CTA of this grid has called it or exited.  Both do nothing in ordinary launches.
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_release() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // Exclusive scan of `value` over the CTA (blockDim.x a multiple of 32, at most
 // 1024); `scratch` holds 33 ints.  Returns the sum of the earlier threads and
 // writes the CTA total to `*total`.  Ends with a barrier.

@@ -506,6 +506,7 @@ __global__ void __launch_bounds__(256) k_adopt(Layer L, Workspace ws, const void
 // shared memory; each thread then finishes 16/CG rows.
 template <int CG>
 __global__ void __launch_bounds__(512) k_screen(Layer L, Workspace ws, const uint8_t* padding, int S) {
+  grid_dependency_release();  // the selection may be scheduled; it waits for this grid
   constexpr int RPT = kWordRows / CG;  // rows a thread finishes per block
   constexpr int U = 8;                 // words in flight per thread
   extern __shared__ int smem[];
@@ -740,6 +741,7 @@ struct GroupFetch {
 // in flight in registers while the current block computes.  Experts with more
 // than eight tokens take further passes of eight, spread over grid.z.
 __global__ void __launch_bounds__(kGroupWarps * 32, 2) k_screen_grouped(Layer L, Workspace ws) {
+  grid_dependency_release();  // the selection may be scheduled; it waits for this grid
   constexpr int kGroupRows = kGroupWarps * 16;  // rows per CTA
   const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
@@ -1279,6 +1281,8 @@ __global__ void __launch_bounds__(kSelectThreads)
     k_select(Layer L, Workspace ws, const uint8_t* padding, int scores_ready, int row_offset,
              typename std::conditional<PEERS, Exchange, NoExchange>::type x) {
   constexpr bool peers = PEERS;
+  grid_dependency_release();  // the exact gather may be scheduled; it waits for this grid
+  grid_dependency_wait();     // the screen's projections are complete
   extern __shared__ uint32_t keys[];
   __shared__ int hist[2048];
   __shared__ int warp_above[33], warp_ties[32];
@@ -1615,6 +1619,7 @@ __device__ __forceinline__ void exact_dot(const uint4* gate, const uint4* up, co
 __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace ws,
                                                             const __nv_bfloat16* hidden,
                                                             const uint8_t* padding) {
+  grid_dependency_wait();  // the selection is complete
   extern __shared__ uint4 xs[];  // H bf16 values of the token
   const int t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (padding && padding[t]) return;
@@ -1679,6 +1684,7 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
 // arithmetic, same order, same bits as k_exact.
 __global__ void __launch_bounds__(kExactWarps * 32) k_exact_pairs(Layer L, Workspace ws,
                                                                   const __nv_bfloat16* hidden) {
+  grid_dependency_wait();  // the selection is complete
   extern __shared__ uint4 xs[];  // H bf16 values of the token
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (static_cast<int>(blockIdx.y) >= ws.group_offsets[L.E]) return;
@@ -2273,6 +2279,31 @@ static int bind_call(const cfm_layer* layer, void* workspace, int32_t capacity,
   return 0;
 }
 
+// Launch with programmatic stream serialisation: the kernel may be scheduled while its
+// predecessor in the stream is finishing and waits for it at grid_dependency_wait().
+// Used for the selection after the screen and for the exact gather after the selection
+// (measured: 0.6 to 1.3 us per call).  CFM_PDL=0 in the environment makes these ordinary
+// launches.
+template <typename... Params, typename... Args>
+static void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, Args... args) {
+  static const bool on = [] {
+    const char* v = std::getenv("CFM_PDL");
+    return !v || std::atoi(v) != 0;
+  }();
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = on ? 1 : 0;
+  (void)cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 static int launched() {
   const cudaError_t err = cudaGetLastError();
   return err == cudaSuccess ? 0 : static_cast<int>(err);
@@ -2400,11 +2431,11 @@ static int run_select(const Bound& b, int scores_ready, const Exchange* exchange
     if (err != cudaSuccess) return static_cast<int>(err);
   }
   if (exchange)
-    k_select<true><<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready,
-                                                            b.row_offset, *exchange);
+    launch_dependent(k_select<true>, dim3(b.T), dim3(kSelectThreads), smem, b.stream, b.L, b.ws,
+                     b.padding, scores_ready, b.row_offset, *exchange);
   else
-    k_select<false><<<b.T, kSelectThreads, smem, b.stream>>>(b.L, b.ws, b.padding, scores_ready,
-                                                             b.row_offset, NoExchange{});
+    launch_dependent(k_select<false>, dim3(b.T), dim3(kSelectThreads), smem, b.stream, b.L, b.ws,
+                     b.padding, scores_ready, b.row_offset, NoExchange{});
   return launched();
 }
 
@@ -2479,8 +2510,8 @@ static int run_exact(const Bound& b, const cfm_call* call) {
     // One warp per kept row of a pair when the pair keeps the mean number of rows.
     const int per_pair = (b.L.F + b.L.K - 1) / b.L.K;
     const int ctas = std::max(1, (per_pair + kExactWarps - 1) / kExactWarps);
-    k_exact_pairs<<<dim3(ctas, b.T * b.L.K), kExactWarps * 32, smem, b.stream>>>(
-        b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden));
+    launch_dependent(k_exact_pairs, dim3(ctas, b.T * b.L.K), dim3(kExactWarps * 32), smem, b.stream,
+                     b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden));
     return launched();
   }
   int ctas = (b.L.F + kExactWarps - 1) / kExactWarps;
@@ -2491,8 +2522,8 @@ static int run_exact(const Bound& b, const cfm_call* call) {
     const int64_t share = (2LL * ctas * b.L.E + b.L.global_experts - 1) / b.L.global_experts;
     ctas = static_cast<int>(std::max<int64_t>(8, std::min<int64_t>(ctas, share)));
   }
-  k_exact<<<dim3(ctas, b.T), kExactWarps * 32, smem,
-            b.stream>>>(b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden), b.padding);
+  launch_dependent(k_exact, dim3(ctas, b.T), dim3(kExactWarps * 32), smem, b.stream, b.L, b.ws,
+                   static_cast<const __nv_bfloat16*>(call->hidden), b.padding);
   return launched();
 }
 

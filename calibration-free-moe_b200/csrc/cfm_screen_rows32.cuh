@@ -28,6 +28,7 @@ constexpr int kRows32Warps = 4;  // 128 rows per CTA, four CTAs per SM
 
 __global__ void __launch_bounds__(kRows32Warps * 32, 16 / kRows32Warps)
     k_screen_rows32(Layer L, Workspace ws) {
+  grid_dependency_release();  // the selection may be scheduled; it waits for this grid
   constexpr int kRows = kRows32Warps * 32;  // rows per CTA
   const int e = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, tq = lane & 3;
