@@ -2054,6 +2054,38 @@ __device__ __forceinline__ int down_slot_end(const Layer& L, const Workspace& ws
 // ---------------------------------------------------------------------------
 // output: router mix + decoder term
 // ---------------------------------------------------------------------------
+// One output column of one token: the per-slot sums of its down-tile partials in
+// tile order, each rounded to BF16 and mixed with the slot's router weight in slot
+// order.  `parts` points at the column in the token's first tile; `slot_end` and
+// `slot_weight` are the token's slot table in shared memory.  Sixteen tile loads are
+// in flight at a time; the additions keep their order.
+__device__ __forceinline__ float mix_down_tiles(const float* parts, int used, size_t stride,
+                                                const int* slot_end, const float* slot_weight) {
+  constexpr int kInFlight = 16;
+  float routed = 0.0f, sum = 0.0f;
+  int slot = 0;
+  for (int base = 0; base < used; base += kInFlight) {
+    float v[kInFlight];
+#pragma unroll
+    for (int j = 0; j < kInFlight; ++j)
+      v[j] = base + j < used ? __ldcg(parts + static_cast<size_t>(base + j) * stride) : 0.0f;
+#pragma unroll
+    for (int j = 0; j < kInFlight; ++j) {
+      const int tile = base + j;
+      if (tile < used) {
+        while (tile >= slot_end[slot]) {  // close the finished slots
+          routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+          sum = 0.0f;
+          ++slot;
+        }
+        sum += v[j];
+      }
+    }
+  }
+  if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+  return routed;
+}
+
 // grid (H / 128, T), 128 threads, one output column per thread.  `fixed` is the
 // number of partial sums per local slot the expert-major down kernel wrote, or 0
 // after the per-token down kernel.
@@ -2076,52 +2108,46 @@ __global__ void __launch_bounds__(128) k_output(Layer L, Workspace ws, const uin
   if (recover)
     for (int r = tid; r < L.R; r += 128)
       latent[r] = bf16_round(ws.latent[static_cast<size_t>(t) * L.R + r]);
-  // The decoder row does not depend on the slot table: fetch it first.
+  // The decoder row does not depend on the slot table: its first chunks are on their
+  // way before the barrier.
+  constexpr int kAhead = 8;  // 16-byte chunks of the decoder row fetched ahead (R <= 64: all)
   float correction = 0.0f;
-  uint4 row[4];
   const uint4* decoder_row = reinterpret_cast<const uint4*>(L.decoder + static_cast<size_t>(h) * L.R);
+  uint4 ahead[kAhead];
+  if (recover) {
+#pragma unroll
+    for (int i = 0; i < kAhead; ++i)
+      ahead[i] = i < L.R / 8 ? decoder_row[i] : make_uint4(0, 0, 0, 0);
+  }
   __syncthreads();
   const int used = slot_end[L.K - 1];  // tiles are laid out slot after slot
-  // Per-slot sums of the tile partials, eight tile loads in flight.
-  const float* parts = ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h;
-  float routed = 0.0f, sum = 0.0f;
-  int slot = 0;
-  for (int base = 0; base < used; base += 8) {
-    float v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = base + j < used ? parts[static_cast<size_t>(base + j) * L.H] : 0.0f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int tile = base + j;
-      if (tile < used) {
-        while (tile >= slot_end[slot]) {  // close the finished slots
-          routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
-          sum = 0.0f;
-          ++slot;
-        }
-        sum += v[j];
-      }
-    }
-  }
-  if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+  const float routed = mix_down_tiles(
+      ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h, used, L.H, slot_end,
+      slot_weight);
   if (recover) {
     float dot = 0.0f;
-    for (int i0 = 0; i0 < L.R / 8; i0 += 4) {
+    auto fold = [&](const uint4 w, int i) {
+      const float* z = latent + i * 8;
+      dot = fmaf(bf16_lo(w.x), z[0], dot);
+      dot = fmaf(bf16_hi(w.x), z[1], dot);
+      dot = fmaf(bf16_lo(w.y), z[2], dot);
+      dot = fmaf(bf16_hi(w.y), z[3], dot);
+      dot = fmaf(bf16_lo(w.z), z[4], dot);
+      dot = fmaf(bf16_hi(w.z), z[5], dot);
+      dot = fmaf(bf16_lo(w.w), z[6], dot);
+      dot = fmaf(bf16_hi(w.w), z[7], dot);
+    };
 #pragma unroll
-      for (int i = 0; i < 4; ++i) row[i] = i0 + i < L.R / 8 ? decoder_row[i0 + i] : make_uint4(0, 0, 0, 0);
+    for (int i = 0; i < kAhead; ++i)
+      if (i < L.R / 8) fold(ahead[i], i);
+    for (int i0 = kAhead; i0 < L.R / 8; i0 += 4) {
+      uint4 row[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        if (i0 + i >= L.R / 8) break;
-        const float* z = latent + (i0 + i) * 8;
-        dot = fmaf(bf16_lo(row[i].x), z[0], dot);
-        dot = fmaf(bf16_hi(row[i].x), z[1], dot);
-        dot = fmaf(bf16_lo(row[i].y), z[2], dot);
-        dot = fmaf(bf16_hi(row[i].y), z[3], dot);
-        dot = fmaf(bf16_lo(row[i].z), z[4], dot);
-        dot = fmaf(bf16_hi(row[i].z), z[5], dot);
-        dot = fmaf(bf16_lo(row[i].w), z[6], dot);
-        dot = fmaf(bf16_hi(row[i].w), z[7], dot);
-      }
+      for (int i = 0; i < 4; ++i)
+        row[i] = i0 + i < L.R / 8 ? decoder_row[i0 + i] : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (i0 + i < L.R / 8) fold(row[i], i0 + i);
     }
     correction = bf16_round(dot);
   }
@@ -2156,19 +2182,9 @@ __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
         slot_weight[tid] = ws.weights[static_cast<size_t>(t) * L.K + tid];
       }
       __syncthreads();
-      const int used = slot_end[L.K - 1];
-      const float* parts = ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h;
-      float sum = 0.0f;
-      int slot = 0;
-      for (int tile = 0; tile < used; ++tile) {
-        while (tile >= slot_end[slot]) {
-          routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
-          sum = 0.0f;
-          ++slot;
-        }
-        sum += parts[static_cast<size_t>(tile) * L.H];
-      }
-      if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
+      routed = mix_down_tiles(
+          ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h, slot_end[L.K - 1], L.H,
+          slot_end, slot_weight);
     }
     routed_out[h] = routed;
     uint32_t* header = exchange_header(x, x.rank);
@@ -2190,20 +2206,9 @@ __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
     slot_weight[tid] = ws.weights[pair];
   }
   __syncthreads();
-  const int used = slot_end[L.K - 1];
-  const float* parts = ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h;
-  float routed = 0.0f, sum = 0.0f;
-  int slot = 0;
-  for (int tile = 0; tile < used; ++tile) {
-    while (tile >= slot_end[slot]) {
-      routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
-      sum = 0.0f;
-      ++slot;
-    }
-    sum += parts[static_cast<size_t>(tile) * L.H];
-  }
-  if (used > 0) routed = fmaf(bf16_round(sum), slot_weight[slot], routed);
-  routed_out[h] = routed;
+  routed_out[h] = mix_down_tiles(
+      ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h, slot_end[L.K - 1], L.H,
+      slot_end, slot_weight);
 }
 
 __global__ void __launch_bounds__(128) k_finish(Layer L, const float* combined,
