@@ -1682,15 +1682,14 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact(Layer L, Workspace w
 // other in time and a row several of them kept comes from HBM once and from L2
 // after that.  The X CTAs of a pair share its kept rows, one warp per row.  Same
 // arithmetic, same order, same bits as k_exact.
-__global__ void __launch_bounds__(kExactWarps * 32) k_exact_pairs(Layer L, Workspace ws,
-                                                                  const __nv_bfloat16* hidden) {
-  grid_dependency_wait();  // the selection is complete
-  extern __shared__ uint4 xs[];  // H bf16 values of the token
+// The kept rows of the y-th pair of the list grouped by expert, for the CTA column
+// blockIdx.x; all threads of the CTA call it with the staged row `xs` free.
+__device__ __forceinline__ void exact_pair(const Layer& L, const Workspace& ws,
+                                           const __nv_bfloat16* hidden, uint4* xs, int y) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  if (static_cast<int>(blockIdx.y) >= ws.group_offsets[L.E]) return;
-  const int pair = ws.group_pairs[blockIdx.y];
+  const int pair = ws.group_pairs[y];
   const int count = ws.counts[pair];
-  if (static_cast<int>(blockIdx.x) * kExactWarps >= count) return;
+  if (static_cast<int>(blockIdx.x) * kExactWarps >= count) return;  // the whole CTA
   const int t = pair / L.K, slot = pair - t * L.K, e = ws.ids[pair];
   const int start = ws.starts[pair];
   const int32_t* list = ws.candidate_ids + static_cast<size_t>(t) * L.F + start;
@@ -1719,6 +1718,24 @@ __global__ void __launch_bounds__(kExactWarps * 32) k_exact_pairs(Layer L, Works
       ws.exact[static_cast<size_t>(t) * 2 * L.F + start + index] = g;
       ws.exact[static_cast<size_t>(t) * 2 * L.F + L.F + start + index] = u;
     }
+  }
+}
+
+// STRIDED: under expert parallelism fewer CTA rows than (token, slot) pairs are launched,
+// since a rank owns few of them; row y then takes pairs y, y + gridDim.y, ...
+template <bool STRIDED>
+__global__ void __launch_bounds__(kExactWarps * 32) k_exact_pairs(Layer L, Workspace ws,
+                                                                  const __nv_bfloat16* hidden) {
+  grid_dependency_wait();  // the selection is complete
+  extern __shared__ uint4 xs[];  // H bf16 values of the token
+  const int pairs = ws.group_offsets[L.E];
+  if (!STRIDED) {
+    if (static_cast<int>(blockIdx.y) < pairs) exact_pair(L, ws, hidden, xs, blockIdx.y);
+    return;
+  }
+  for (int y = blockIdx.y; y < pairs; y += gridDim.y) {
+    exact_pair(L, ws, hidden, xs, y);
+    __syncthreads();  // the staged row may be overwritten by the next pair
   }
 }
 
@@ -1898,11 +1915,13 @@ __global__ void __launch_bounds__(128, 4) k_down_tiles(Layer L, Workspace ws) {
   extern __shared__ __align__(128) uint8_t down_ring[];
   __shared__ int tile_channel[kDownTileRows];
   __shared__ float tile_activation[kDownTileRows];
-  if (static_cast<int>(blockIdx.y) >= ws.tile_count[0]) return;
-  const int4* record = reinterpret_cast<const int4*>(ws.tile_list) + 2 * blockIdx.y;
-  const int4 a = record[0], b = record[1];  // t, slot, expert, rows | list, tile
-  down_tile<STAGES>(L, ws, a.x, a.y, a.z, a.w, ws.candidate_ids + b.x, b.y, tile_channel,
-            tile_activation, down_ring);
+  const int tiles = ws.tile_count[0];
+  for (int y = blockIdx.y; y < tiles; y += gridDim.y) {  // strides under expert parallelism
+    const int4* record = reinterpret_cast<const int4*>(ws.tile_list) + 2 * y;
+    const int4 a = record[0], b = record[1];  // t, slot, expert, rows | list, tile
+    down_tile<STAGES>(L, ws, a.x, a.y, a.z, a.w, ws.candidate_ids + b.x, b.y, tile_channel,
+                      tile_activation, down_ring);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -2086,6 +2105,45 @@ __device__ __forceinline__ float mix_down_tiles(const float* parts, int used, si
   return routed;
 }
 
+// The same for four adjacent columns (16-byte loads); each column's additions keep
+// the order of the one-column version.
+__device__ __forceinline__ float4 mix_down_tiles4(const float* parts, int used, size_t stride,
+                                                  const int* slot_end, const float* slot_weight) {
+  constexpr int kInFlight = 8;
+  float4 routed = make_float4(0.0f, 0.0f, 0.0f, 0.0f), sum = routed;
+  int slot = 0;
+  auto close = [&]() {
+    const float w = slot_weight[slot];
+    routed.x = fmaf(bf16_round(sum.x), w, routed.x);
+    routed.y = fmaf(bf16_round(sum.y), w, routed.y);
+    routed.z = fmaf(bf16_round(sum.z), w, routed.z);
+    routed.w = fmaf(bf16_round(sum.w), w, routed.w);
+    sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    ++slot;
+  };
+  for (int base = 0; base < used; base += kInFlight) {
+    float4 v[kInFlight];
+#pragma unroll
+    for (int j = 0; j < kInFlight; ++j)
+      v[j] = base + j < used
+                 ? __ldcg(reinterpret_cast<const float4*>(parts + static_cast<size_t>(base + j) * stride))
+                 : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+    for (int j = 0; j < kInFlight; ++j) {
+      const int tile = base + j;
+      if (tile < used) {
+        while (tile >= slot_end[slot]) close();  // close the finished slots
+        sum.x += v[j].x;
+        sum.y += v[j].y;
+        sum.z += v[j].z;
+        sum.w += v[j].w;
+      }
+    }
+  }
+  if (used > 0) close();
+  return routed;
+}
+
 // grid (H / 128, T), 128 threads, one output column per thread.  `fixed` is the
 // number of partial sums per local slot the expert-major down kernel wrote, or 0
 // after the per-token down kernel.
@@ -2171,22 +2229,26 @@ __global__ void __launch_bounds__(128) k_partial_output(Layer L, Workspace ws,
   float* routed_out = combined + static_cast<size_t>(t) * (L.H + L.R);
   const bool padded = padding && padding[t];
   if (peers) {
+    // grid (ceil(H / 512), T): four adjacent columns per thread, so that a row crosses
+    // NVLink in 16-byte stores and a quarter of the CTAs fence and arrive.
+    const int h4 = (blockIdx.x * 128 + tid) * 4;
     const int home = t / x.tokens, row = t - home * x.tokens;
     routed_out = reinterpret_cast<float*>(x.block[home] +
                                           exchange_rows_offset(x.world, x.tokens, L.F)) +
                  (static_cast<size_t>(x.rank) * x.tokens + row) * L.H;
-    float routed = 0.0f;
+    float4 routed = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (!padded) {
       if (tid < L.K) {
         slot_end[tid] = down_slot_end(L, ws, t, tid, fixed);
         slot_weight[tid] = ws.weights[static_cast<size_t>(t) * L.K + tid];
       }
       __syncthreads();
-      routed = mix_down_tiles(
-          ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h, slot_end[L.K - 1], L.H,
-          slot_end, slot_weight);
+      if (h4 < L.H)
+        routed = mix_down_tiles4(
+            ws.down_parts + static_cast<size_t>(t) * ws.down_tiles * L.H + h4, slot_end[L.K - 1],
+            L.H, slot_end, slot_weight);
     }
-    routed_out[h] = routed;
+    if (h4 < L.H) *reinterpret_cast<float4*>(routed_out + h4) = routed;
     uint32_t* header = exchange_header(x, x.rank);
     exchange_announce(header + kExchangeRowsArrive + home, gridDim.x * x.tokens,
                       exchange_header(x, home) + kExchangeRowsFlag + x.rank,
@@ -2507,7 +2569,11 @@ static int run_exact(const Bound& b, const cfm_call* call) {
     cudaError_t err = cudaFuncSetAttribute(
         k_exact, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
     if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(k_exact_pairs, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      err = cudaFuncSetAttribute(k_exact_pairs<false>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem));
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(k_exact_pairs<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem));
     if (err != cudaSuccess) return static_cast<int>(err);
   }
@@ -2515,8 +2581,19 @@ static int run_exact(const Bound& b, const cfm_call* call) {
     // One warp per kept row of a pair when the pair keeps the mean number of rows.
     const int per_pair = (b.L.F + b.L.K - 1) / b.L.K;
     const int ctas = std::max(1, (per_pair + kExactWarps - 1) / kExactWarps);
-    launch_dependent(k_exact_pairs, dim3(ctas, b.T * b.L.K), dim3(kExactWarps * 32), smem, b.stream,
-                     b.L, b.ws, static_cast<const __nv_bfloat16*>(call->hidden));
+    int64_t rows = static_cast<int64_t>(b.T) * b.L.K;
+    if (b.L.expert_map && b.L.global_experts > 0)  // twice the expected share of the pairs
+      rows = std::max<int64_t>(8, std::min<int64_t>(
+                                      rows, (2 * rows * b.L.E + b.L.global_experts - 1) /
+                                                b.L.global_experts));
+    if (rows < static_cast<int64_t>(b.T) * b.L.K)
+      launch_dependent(k_exact_pairs<true>, dim3(ctas, static_cast<unsigned>(rows)),
+                       dim3(kExactWarps * 32), smem, b.stream, b.L, b.ws,
+                       static_cast<const __nv_bfloat16*>(call->hidden));
+    else
+      launch_dependent(k_exact_pairs<false>, dim3(ctas, static_cast<unsigned>(rows)),
+                       dim3(kExactWarps * 32), smem, b.stream, b.L, b.ws,
+                       static_cast<const __nv_bfloat16*>(call->hidden));
     return launched();
   }
   int ctas = (b.L.F + kExactWarps - 1) / kExactWarps;
@@ -2554,8 +2631,12 @@ static int run_down(const Bound& b) {
   }
   if (pairs_grouped(b)) {
     // The call's tiles were listed in expert order after the selection.
-    const int most = b.T * ((b.L.F + kDownTileRows - 1) / kDownTileRows + b.L.K);
-    const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, most);
+    int64_t most = static_cast<int64_t>(b.T) * ((b.L.F + kDownTileRows - 1) / kDownTileRows + b.L.K);
+    if (b.L.expert_map && b.L.global_experts > 0)  // twice the expected share of the tiles
+      most = std::max<int64_t>(8, std::min<int64_t>(
+                                      most, (2 * most * b.L.E + b.L.global_experts - 1) /
+                                                b.L.global_experts));
+    const dim3 grid((b.L.H + kDownColumns - 1) / kDownColumns, static_cast<unsigned>(most));
     return launch_down([&](auto stages) {
       constexpr int S = decltype(stages)::value;
       cudaError_t err = cudaFuncSetAttribute(
@@ -2747,7 +2828,7 @@ int cfm_partial_output(const cfm_layer* layer, void* workspace, int32_t capacity
   } else if (!call->out) {
     return CFM_E_NULL;
   }
-  k_partial_output<<<dim3(b.L.H / 128, b.T), 128, 0, b.stream>>>(
+  k_partial_output<<<dim3(peers ? (b.L.H + 511) / 512 : b.L.H / 128, b.T), 128, 0, b.stream>>>(
       b.L, b.ws, b.padding, static_cast<float*>(call->out),
       rows_grouped(b) ? down_grouped_parts(b) : 0, x, peers);
   return launched();

@@ -140,8 +140,14 @@ def test_sharded_reader_matches_single_gpu(name, strategy, exchange):
     world = 2
     manager = mp.Manager()
     results = manager.dict()
-    mp.spawn(_worker, args=(world, _free_port(), name, strategy, exchange, results), nprocs=world,
-             join=True)
+    for attempt in range(3):  # the probed port can be taken again before rank 0 listens on it
+        try:
+            mp.spawn(_worker, args=(world, _free_port(), name, strategy, exchange, results),
+                     nprocs=world, join=True)
+            break
+        except Exception as error:
+            if "EADDRINUSE" not in str(error) or attempt == 2:
+                raise
     case = prepared(name)["case"]
     reference, kept, scores, selected = results[0][6]
     tokens = case.hidden.shape[0] // world
